@@ -1,0 +1,151 @@
+// Shared device helpers for the sm_100a kernels of offload_adam_b200.
+//
+// Everything here is bit-level arithmetic on bf16/fp32 patterns plus small
+// vector load/store wrappers.  The float math uses the explicit round-to-nearest
+// intrinsics (__fadd_rn, __fmul_rn, ...) which the compiler never contracts into
+// FMAs, so each kernel reproduces an op-by-op fp32 PyTorch restatement of the
+// same formula bit for bit.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace oab {
+
+// ----------------------------------------------------------------------------
+// launch accounting: every wrapper that launches one of our kernels bumps this
+// counter so the benchmark can report how many of our launches ran in a region.
+// ----------------------------------------------------------------------------
+extern unsigned long long g_launch_count;
+inline void count_launch(unsigned long long n = 1) { g_launch_count += n; }
+
+// ----------------------------------------------------------------------------
+// bf16 <-> fp32 bit helpers
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b16) {
+  return __uint_as_float(b16 << 16);
+}
+
+// round-to-nearest-even fp32 -> bf16 bit pattern (NaN quieted like torch).
+__device__ __forceinline__ uint32_t f32_to_bf16_rne_bits(float f) {
+  uint32_t u = __float_as_uint(f);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return 0x7fc0u;  // NaN
+  uint32_t lsb = (u >> 16) & 1u;
+  u += 0x7fffu + lsb;
+  return u >> 16;
+}
+
+// 16 random bits decide whether the truncated bf16 moves one step away from
+// zero: up iff rand16 < low 16 bits of the fp32 pattern.
+__device__ __forceinline__ uint32_t f32_to_bf16_sr_bits(float f, uint32_t rand16) {
+  uint32_t u = __float_as_uint(f);
+  uint32_t frac = u & 0xffffu;
+  uint32_t trunc = u & 0xffff0000u;
+  uint32_t r = (rand16 < frac) ? (trunc + 0x10000u) : trunc;
+  return r >> 16;
+}
+
+// ----------------------------------------------------------------------------
+// Philox4x32-10: counter = (ctr_lo, ctr_hi, 0, 0), key = (seed_lo, seed_hi).
+// One call yields 128 random bits = eight 16-bit words, enough for one 8-wide
+// bf16 vector.  The CPU restatement in ops/oracle.py generates the same stream.
+// ----------------------------------------------------------------------------
+struct Philox4 {
+  uint32_t x, y, z, w;
+};
+
+__host__ __device__ __forceinline__ Philox4 philox4x32_10(uint64_t counter, uint64_t seed) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u;
+  const uint32_t W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+  uint32_t c0 = (uint32_t)counter, c1 = (uint32_t)(counter >> 32), c2 = 0u, c3 = 0u;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    uint64_t p0 = (uint64_t)M0 * c0;
+    uint64_t p1 = (uint64_t)M1 * c2;
+    uint32_t hi0 = (uint32_t)(p0 >> 32), lo0 = (uint32_t)p0;
+    uint32_t hi1 = (uint32_t)(p1 >> 32), lo1 = (uint32_t)p1;
+    uint32_t n0 = hi1 ^ c1 ^ k0;
+    uint32_t n1 = lo1;
+    uint32_t n2 = hi0 ^ c3 ^ k1;
+    uint32_t n3 = lo0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += W0; k1 += W1;
+  }
+  Philox4 out{c0, c1, c2, c3};
+  return out;
+}
+
+// ----------------------------------------------------------------------------
+// 16-byte vector I/O.  The *_stream variants carry cache hints for data touched
+// exactly once (optimizer state): they bypass L1 allocation.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld16(const void* p) {
+  return *reinterpret_cast<const uint4*>(p);
+}
+__device__ __forceinline__ void st16(void* p, uint4 v) {
+  *reinterpret_cast<uint4*>(p) = v;
+}
+__device__ __forceinline__ uint4 ld16_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st16_stream(void* p, uint4 v) {
+  asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ bool aligned16(const void* p) {
+  return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+// block-wide sum in a fixed tree order (deterministic for a given blockDim).
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* smem /* >= THREADS/32 floats */) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float r = 0.f;
+  if (warp == 0) {
+    r = (lane < THREADS / 32) ? smem[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  }
+  __syncthreads();
+  return r;  // valid in warp 0 (all lanes)
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* smem) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float r = 0.f;
+  if (warp == 0) {
+    r = (lane < THREADS / 32) ? smem[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, o));
+  }
+  __syncthreads();
+  return r;
+}
+
+// Number of SMs on a B200; grids are sized as multiples of this.
+constexpr int kNumSMs = 148;
+
+// Status codes written by kernels that can give up on a bounded wait.
+enum Status : int {
+  kStatusOk = 0,
+  kStatusTimeout = 1,
+  kStatusBadArg = 2,
+};
+
+}  // namespace oab

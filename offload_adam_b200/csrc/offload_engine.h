@@ -1,0 +1,93 @@
+// Copy engine for optimizer state that lives in pinned host memory.
+//
+// Two ways of moving state through the step are provided; both run entirely on
+// side streams so that they overlap the rest of backward:
+//
+//  * staged: each tensor is cut into fixed-size chunks that flow through a
+//    ring of device slots: H2D (copy stream A) -> kernel (compute stream) ->
+//    D2H (copy stream B).  Three chunks are in flight at any time, so both DMA
+//    directions and the SMs work concurrently and device memory use is bounded
+//    by slots * chunk bytes, independent of tensor size.
+//  * zero-copy: the kernel reads and writes the mapped host buffers itself; no
+//    staging memory at all (see adam_step.h).  Issued directly by the caller.
+//
+// The reference moves whole tensors with one `.to(device)` / `copy_` per state
+// on two side streams whose H2D side waits for the main stream at every hook
+// (reference: src/offload_adam/offload_adam.py:347-372), so a transfer can
+// neither start early nor overlap the kernel of the previous tensor.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <vector>
+
+#include "adam_step.h"
+
+namespace oab {
+
+struct EngineOptions {
+  int64_t chunk_elems = int64_t(8) << 20;  // elements per staged chunk
+  int slots = 4;                           // ring depth
+  int max_ctas = 0;                        // grid cap for kernels on the compute stream
+};
+
+struct StagedStepArgs {
+  int pid = -1;          // slot in the per-tensor "host copy is up to date" event table
+  AdamStepArgs k;        // p and (optionally) g are device pointers for the whole tensor;
+                         // m/v/extra are the HOST pointers of the state
+  const void* host_grad = nullptr;  // optional host-resident accumulated gradient
+                                    // (added to k.g as the kernel's second term, or used
+                                    // alone when k.g == nullptr)
+};
+
+class OffloadEngine {
+ public:
+  // `workspace` must hold workspace_bytes(opt) of device memory.
+  OffloadEngine(int device, cudaStream_t compute, cudaStream_t h2d, cudaStream_t d2h,
+                void* workspace, size_t workspace_bytes, const EngineOptions& opt, int n_tensors);
+  ~OffloadEngine();
+  static size_t workspace_bytes(const EngineOptions& opt);
+
+  // Adam step of one tensor through the slot ring.  The caller has already made
+  // the compute stream wait for the gradient producer.
+  void staged_step(const StagedStepArgs& a);
+
+  // host_grad (+)= dev_grad through the ring, optionally producing sum of squares of
+  // the result into *sumsq_out (device pointer).  first == true: plain D2H copy.
+  void staged_grad_to_host(int pid, void* host_grad, const void* dev_grad, int64_t n, bool first,
+                           float* sumsq_out, float* scratch);
+
+  // Makes `stream` wait until every transfer/kernel enqueued so far has finished.
+  void join(cudaStream_t stream);
+  // Blocks the host until the engine streams are idle.
+  void synchronize();
+
+  int64_t bytes_h2d() const { return bytes_h2d_; }
+  int64_t bytes_d2h() const { return bytes_d2h_; }
+  void reset_counters() { bytes_h2d_ = bytes_d2h_ = 0; }
+
+ private:
+  struct Slot {
+    char* base = nullptr;
+    cudaEvent_t h2d_done = nullptr, k_done = nullptr, free_ev = nullptr;
+    bool used = false;
+  };
+  Slot& next_slot();
+  void check(cudaError_t e, const char* what);
+
+  int device_;
+  cudaStream_t compute_, h2d_, d2h_;
+  EngineOptions opt_;
+  std::vector<Slot> slots_;
+  size_t slot_bytes_ = 0;
+  int cursor_ = 0;
+  std::vector<cudaEvent_t> host_ready_;  // per tensor: last D2H of its state finished
+  std::vector<char> host_ready_set_;
+  std::vector<cudaEvent_t> grad_ready_;  // per tensor: last D2H of its host gradient finished
+  std::vector<char> grad_ready_set_;
+  cudaEvent_t tmp_ev_ = nullptr;
+  cudaEvent_t join_ev_[3] = {nullptr, nullptr, nullptr};
+  int64_t bytes_h2d_ = 0, bytes_d2h_ = 0;
+};
+
+}  // namespace oab
