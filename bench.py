@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Headline benchmark: Llama-3-8B-shaped full-parameter training with host-offloaded Adam.
+
+    python bench.py --gpus 1 --steps K --warmup W                 # this framework
+    python bench.py --impl reference --gpus 1 --steps K --warmup W  # unmodified reference
+
+For N > 1 launch with ``python -m torch.distributed.run --nnodes=1 --nproc-per-node N
+--master-addr 127.0.0.1 --master-port P bench.py --gpus N ...`` (one rank per GPU).
+
+Metric: training tokens/s of the whole job (all ranks), Llama-3-8B shape, synthetic
+uniform tokens, random-init bf16 weights, ``DistributedOffloadAdam`` ZeRO-1,
+mode=fp32_master, max_grad_norm=1.0, AdamW wd 0.01, lr 1e-4, per-rank micro-batch
+1 x 4096, 4 accumulation micro-batches per optimizer step.  ``--preset single`` selects
+the single-GPU stochastic-rounding configuration (OffloadAdam, no clipping, 8
+micro-batches).  Rank 0 prints one JSON line.
+
+Timing: W untimed warm-up steps, then exactly K steps between a barrier +
+``torch.cuda.synchronize()`` on both sides, measured with CUDA events on the main
+stream, max over ranks.  The working set (16 GB of parameters plus activations) is far
+larger than L2, so no explicit L2 flush is needed between iterations.  ``value`` is the
+device-timed number with inputs already on the GPU; ``e2e`` repeats the measurement
+through the public API with every micro-batch's token ids copied from pinned host
+memory and the step's loss read back to the host.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import socket
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+PRESETS = {
+    # BASELINE config 3: ZeRO-1 fp32_master + clipping at 1/2/4/8 GPUs
+    "zero1": dict(optimizer="distributed", mode="fp32_master", max_grad_norm=1.0, ga=4,
+                  weight_decay=0.01, lr=1e-4, seq=4096, mb=1),
+    # BASELINE config 2: single-GPU stochastic rounding, step inside backward
+    "single": dict(optimizer="offload", mode="stochastic_rounding", max_grad_norm=None, ga=8,
+                   weight_decay=0.01, lr=1e-4, seq=4096, mb=1),
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--preset", choices=list(PRESETS), default="zero1")
+    ap.add_argument("--model", choices=["llama3-8b", "llama3-70b", "tiny"], default="llama3-8b")
+    ap.add_argument("--layers", type=int, default=None, help="debug only: override layer count")
+    ap.add_argument("--seq", type=int, default=None)
+    ap.add_argument("--ga", type=int, default=None)
+    ap.add_argument("--mode", default=None)
+    ap.add_argument("--transfer", default="auto")
+    ap.add_argument("--grad-residency", default="auto")
+    ap.add_argument("--comm", default="auto", help="distributed path: auto | symm | nccl")
+    ap.add_argument("--max-ctas", type=int, default=0)
+    ap.add_argument("--grad-ckpt", action="store_true", help="activation checkpointing per layer")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--verbose", type=int, default=0)
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- utils
+def setup_dist(n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != n_gpus:
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    if "MASTER_ADDR" not in os.environ:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+    if "MASTER_PORT" not in os.environ:
+        s = socket.socket()
+        s.bind(("127.0.0.1", 0))
+        os.environ["MASTER_PORT"] = str(s.getsockname()[1])
+        s.close()
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", local_rank))
+    return rank, local_rank, world
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during a region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        try:
+            rows = [r.strip().split(",") for r in open(self.path) if r.strip()]
+            os.unlink(self.path)
+        except Exception:
+            return out
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.strip().lower() == "active":
+                    reasons.add(name)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                       samples=len(sm))
+        return out
+
+
+def max_over_ranks(x, device):
+    t = torch.tensor([float(x)], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+# ------------------------------------------------------------------ model builders
+def model_dims(args):
+    from offload_adam_b200.models.llama import llama3_8b, llama3_70b, tiny_llama
+    cfg = {"llama3-8b": llama3_8b, "llama3-70b": llama3_70b, "tiny": tiny_llama}[args.model]()
+    if args.layers is not None:
+        cfg.num_layers = args.layers
+    return cfg
+
+
+def build_ours(args, preset, device):
+    from offload_adam_b200 import DistributedOffloadAdam, OffloadAdam
+    from offload_adam_b200.models.llama import build_llama
+    cfg = model_dims(args)
+    model = build_llama(cfg, device=device, dtype=torch.bfloat16, seed=0)
+    model.train()
+    if args.grad_ckpt:
+        model.gradient_checkpointing_enable()
+    common = dict(lr=preset["lr"], betas=(0.9, 0.999), eps=1e-8, weight_decay=preset["weight_decay"],
+                  mode=preset["mode"], decoupled_weight_decay=True, max_grad_norm=preset["max_grad_norm"],
+                  verbose=args.verbose, transfer=args.transfer, grad_residency=args.grad_residency,
+                  max_ctas=args.max_ctas, seed=1234)
+    if preset["optimizer"] == "distributed":
+        opt = DistributedOffloadAdam(model, comm=args.comm, **common)
+    else:
+        opt = OffloadAdam(model, **common)
+
+    def loss_fn(ids):
+        return model(ids, labels=ids)
+
+    return model, opt, loss_fn, cfg.vocab_size
+
+
+def build_reference(args, preset, device):
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    import offload_adam as ref  # the unmodified reference package
+    from transformers import LlamaConfig, LlamaForCausalLM
+    d = model_dims(args)
+    hf = LlamaConfig(vocab_size=d.vocab_size, hidden_size=d.hidden_size, intermediate_size=d.intermediate_size,
+                     num_hidden_layers=d.num_layers, num_attention_heads=d.num_heads,
+                     num_key_value_heads=d.num_kv_heads, rope_theta=d.rope_theta, rms_norm_eps=d.rms_eps,
+                     tie_word_embeddings=d.tie_embeddings, max_position_embeddings=max(8192, preset["seq"]),
+                     attn_implementation="sdpa", use_cache=False, initializer_range=0.02)
+    torch.manual_seed(0)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(device):
+            model = LlamaForCausalLM(hf)
+    finally:
+        torch.set_default_dtype(prev)
+    model = model.to(torch.bfloat16)
+    model.config.use_cache = False
+    model.train()
+    if args.grad_ckpt:
+        model.gradient_checkpointing_enable()
+    common = dict(lr=preset["lr"], betas=(0.9, 0.999), eps=1e-8, weight_decay=preset["weight_decay"],
+                  mode=preset["mode"], decoupled_weight_decay=True, max_grad_norm=preset["max_grad_norm"],
+                  verbose=args.verbose)
+    if preset["optimizer"] == "distributed":
+        opt = ref.DistributedOffloadAdam(model, **common)
+    else:
+        opt = ref.OffloadAdam(model, **common)
+
+    def loss_fn(ids):
+        return model(input_ids=ids, labels=ids).loss
+
+    return model, opt, loss_fn, d.vocab_size
+
+
+# ------------------------------------------------------------------------ training
+def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, device=None,
+              exposed=None):
+    """One entry of ``batches_*`` per micro-batch (cycled).  With ``batches_host`` the
+    ids are copied from pinned memory every micro-batch and the loss is read back every
+    step (end-to-end mode)."""
+    last = None
+    k = 0
+    for _ in range(n_steps):
+        for micro in range(ga):
+            opt.ready_for_optimizer_step = micro == ga - 1
+            if batches_host is not None:
+                ids = batches_host[k % len(batches_host)].to(device, non_blocking=True)
+            else:
+                ids = batches_dev[k % len(batches_dev)]
+            k += 1
+            loss = loss_fn(ids)
+            (loss / ga).backward()
+            last = loss.detach()
+        if exposed is not None:
+            e0 = torch.cuda.Event(enable_timing=True); e0.record()
+        opt.step()
+        if exposed is not None:
+            e1 = torch.cuda.Event(enable_timing=True); e1.record()
+            exposed.append((e0, e1))
+        if batches_host is not None:
+            last = last.float().item()  # device -> host read of the step's result
+    return last
+
+
+def timed(fn, device):
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    out = fn()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    wall = time.perf_counter() - t0
+    return e0.elapsed_time(e1), wall * 1e3, out
+
+
+def main():
+    args = parse_args()
+    preset = dict(PRESETS[args.preset])
+    for k in ("seq", "ga", "mode"):
+        if getattr(args, k) is not None:
+            preset[k] = getattr(args, k)
+    if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "offload_adam")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed"}))
+        return 0
+    rank, local_rank, world = setup_dist(args.gpus)
+    device = torch.device("cuda", local_rank)
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cudnn.allow_tf32 = True
+
+    build = build_ours if args.impl == "ours" else build_reference
+    t_build = time.perf_counter()
+    model, opt, loss_fn, vocab = build(args, preset, device)
+    torch.cuda.synchronize()
+    t_build = time.perf_counter() - t_build
+
+    ga, seq, mb = preset["ga"], preset["seq"], preset["mb"]
+    gen = torch.Generator().manual_seed(1000 + rank)
+    host_batches = [torch.randint(0, vocab, (mb, seq), generator=gen, dtype=torch.long).pin_memory()
+                    for _ in range(ga * 2)]
+    dev_batches = [b.to(device) for b in host_batches]
+    tokens_per_step = mb * seq * ga * world
+
+    launches0 = None
+    if args.impl == "ours":
+        from offload_adam_b200 import _ext
+        C = _ext.load(required=True)
+
+    # warm-up (also compiles/loads every kernel)
+    run_steps(args.warmup, ga, opt, loss_fn, batches_dev=dev_batches)
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    if args.impl == "ours":
+        launches0 = C.launch_count()
+    exposed = []
+    ms, wall_ms, _ = timed(lambda: run_steps(args.steps, ga, opt, loss_fn, batches_dev=dev_batches,
+                                             exposed=exposed), device)
+    launches = (C.launch_count() - launches0) if launches0 is not None else None
+    clocks = sampler.stop()
+    exposed_ms = statistics.mean(a.elapsed_time(b) for a, b in exposed) if exposed else None
+    ms = max_over_ranks(ms, device)
+    exposed_ms = max_over_ranks(exposed_ms, device)
+    peak_gb = torch.cuda.max_memory_allocated() / 1024**3
+
+    e2e = None
+    if not args.skip_e2e:
+        ms2, wall2, last_loss = timed(lambda: run_steps(args.steps, ga, opt, loss_fn,
+                                                        batches_host=host_batches, device=device), device)
+        ms2 = max_over_ranks(max(ms2, 0.0), device)
+        wall2 = max_over_ranks(wall2, device)
+        # the loss read-back makes the host wait for the device, so wall time and
+        # event time agree; report the larger of the two
+        t = max(ms2, wall2)
+        e2e = {"value": tokens_per_step * args.steps / (t / 1e3), "unit": "tokens/s",
+               "h2d_bytes_per_step": ga * mb * seq * 8, "d2h_bytes_per_step": 4,
+               "ms_per_step": t / args.steps, "loss": last_loss}
+
+    if rank == 0:
+        value = tokens_per_step * args.steps / (ms / 1e3)
+        out = {
+            "metric": "tokens/s (max over ranks) 8B-shape offload Adam",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic uniform token ids; random-init weights N(0,0.02)",
+            "impl": args.impl,
+            "config": {
+                "model": args.model + (f"-{args.layers}layers" if args.layers else ""),
+                "global_batch": mb * ga * world, "seq_len": seq,
+                "parallelism": f"zero1-dp{world}" if preset["optimizer"] == "distributed" else "single",
+                "optimizer": ("DistributedOffloadAdam" if preset["optimizer"] == "distributed" else "OffloadAdam"),
+                "mode": preset["mode"], "max_grad_norm": preset["max_grad_norm"],
+                "grad_accum": ga, "micro_batch": mb, "activation_checkpointing": bool(args.grad_ckpt),
+                "l2_policy": "inputs larger than L2 (16 GB of parameters per step)",
+                "transfer": getattr(opt, "transfer", None),
+                "grad_residency": getattr(opt, "grad_residency", "host (reference)"),
+                "comm": getattr(opt, "comm", None),
+            },
+            "exposed_opt_ms": exposed_ms, "peak_gpu_gb": peak_gb, "build_s": t_build,
+            "wall_ms_per_step": wall_ms / args.steps, "clocks": clocks,
+            "e2e": e2e, "gpu_launches": launches,
+        }
+        print(json.dumps(out))
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

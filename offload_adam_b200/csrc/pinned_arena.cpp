@@ -10,8 +10,7 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
-#include <fstream>
-#include <sstream>
+#include <cstdio>
 #include <stdexcept>
 #include <thread>
 
@@ -72,22 +71,22 @@ double now_s() {
 size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 int64_t read_meminfo_field(int node, const char* field) {
-  std::ostringstream path;
-  path << "/sys/devices/system/node/node" << node << "/meminfo";
-  std::ifstream f(path.str());
+  // plain stdio: "Node 1 MemFree:   64457228 kB"
+  char path[128];
+  snprintf(path, sizeof(path), "/sys/devices/system/node/node%d/meminfo", node);
+  FILE* f = fopen(path, "r");
   if (!f) return -1;
-  std::string line;
-  while (std::getline(f, line)) {
-    if (line.find(field) == std::string::npos) continue;
-    // "Node 1 MemFree:   64457228 kB"
-    std::istringstream ls(line);
-    std::vector<std::string> tok;
-    std::string t;
-    while (ls >> t) tok.push_back(t);
-    if (tok.size() < 2) return -1;
-    try { return std::stoll(tok[tok.size() - 2]) * 1024; } catch (...) { return -1; }
+  char line[256];
+  int64_t out = -1;
+  while (fgets(line, sizeof(line), f)) {
+    const char* hit = strstr(line, field);
+    if (!hit) continue;
+    long long kb = 0;
+    if (sscanf(hit + strlen(field), " %lld", &kb) == 1) out = (int64_t)kb * 1024;
+    break;
   }
-  return -1;
+  fclose(f);
+  return out;
 }
 
 }  // namespace
@@ -212,9 +211,12 @@ std::string pci_bus_id(int device) {
 int gpu_numa_node(int device) {
   std::string pci = pci_bus_id(device);
   if (pci.empty()) return -1;
-  std::ifstream f("/sys/bus/pci/devices/" + pci + "/numa_node");
+  std::string path = "/sys/bus/pci/devices/" + pci + "/numa_node";
+  FILE* f = fopen(path.c_str(), "r");
+  if (!f) return -1;
   int node = -1;
-  if (!(f >> node)) return -1;
+  if (fscanf(f, "%d", &node) != 1) node = -1;
+  fclose(f);
   return node;
 }
 
@@ -224,9 +226,9 @@ int64_t numa_node_total_bytes(int node) { return read_meminfo_field(node, "MemTo
 int numa_num_nodes() {
   int n = 0;
   for (int i = 0; i < 1024; ++i) {
-    std::ostringstream p;
-    p << "/sys/devices/system/node/node" << i;
-    if (access(p.str().c_str(), F_OK) == 0) ++n; else if (i > 64) break;
+    char path[96];
+    snprintf(path, sizeof(path), "/sys/devices/system/node/node%d", i);
+    if (access(path, F_OK) == 0) ++n; else if (i > 64) break;
   }
   return n;
 }

@@ -1,0 +1,172 @@
+"""Transfer layer of the offloaded optimizers.
+
+``TransferEngine`` owns the side streams and hides *how* optimizer state that
+lives in pinned host memory meets the gradient on the GPU:
+
+``zero_copy``  the step kernel reads and writes the mapped host buffers itself,
+               over PCIe, in one launch per tensor; no staging memory.
+``staged``     the C++ copy engine (csrc/offload_engine.cpp) cuts a tensor into
+               chunks and pipelines H2D -> kernel -> D2H through a ring of
+               device slots on three streams.
+``host``       CPU tensors: everything is synchronous PyTorch (unit tests,
+               gloo multi-process tests).
+
+All work is enqueued on side streams ordered after the main stream's current
+position; nothing blocks the host except the bounded back-pressure on queued
+gradient bytes.  The reference does the same job with whole-tensor
+``.to(device)`` / ``copy_`` calls on two streams plus per-parameter events
+(reference: src/offload_adam/offload_adam.py:344-382).
+"""
+
+from __future__ import annotations
+
+import collections
+
+import torch
+
+from . import _ext
+from .ops import grad_ops
+from .ops.adam_step import adam_step
+from .ops.oracle import MODE_IDS, beta_hat
+
+
+class TransferEngine:
+    def __init__(self, device, mode, n_tensors, transfer="auto", chunk_elems=8 << 20, ring_slots=4,
+                 max_ctas=0, max_inflight_bytes=8 << 30):
+        self.device = torch.device(device)
+        self.mode = mode
+        self.mode_id = MODE_IDS[mode]
+        self.cuda = self.device.type == "cuda"
+        if not self.cuda:
+            transfer = "host"
+        elif transfer == "auto":
+            transfer = "zero_copy"
+        if transfer not in ("zero_copy", "staged", "host"):
+            raise ValueError(f"transfer must be 'auto', 'zero_copy' or 'staged' (got {transfer!r})")
+        self.transfer = transfer
+        self.max_ctas = int(max_ctas)
+        self.max_inflight_bytes = int(max_inflight_bytes)
+        self._inflight = collections.deque()  # (event, nbytes)
+        self._inflight_bytes = 0
+        self.h2d_stream = self.d2h_stream = self.opt_stream = None
+        self._native = None
+        self.scratch = None
+        if self.cuda:
+            self.C = _ext.load(required=True)
+            with torch.cuda.device(self.device):
+                self.opt_stream = torch.cuda.Stream()
+                self.h2d_stream = torch.cuda.Stream()
+                self.d2h_stream = torch.cuda.Stream()
+                self.scratch = grad_ops.sumsq_scratch(self.device)
+                if transfer == "staged":
+                    nbytes = self.C.OffloadEngine.workspace_bytes(chunk_elems, ring_slots)
+                    ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+                    self._native = self.C.OffloadEngine(
+                        self.device.index or 0, self.opt_stream.cuda_stream,
+                        self.h2d_stream.cuda_stream, self.d2h_stream.cuda_stream, ws,
+                        chunk_elems, ring_slots, self.max_ctas, n_tensors,
+                    )
+
+    # ------------------------------------------------------------ stream glue
+    def fork_from_main(self):
+        """Side work enqueued after this call starts after everything already on
+        the main stream."""
+        if self.cuda:
+            self.opt_stream.wait_stream(torch.cuda.current_stream(self.device))
+
+    def join_main(self):
+        """The main stream waits for every side-stream operation enqueued so far."""
+        if not self.cuda:
+            return
+        main = torch.cuda.current_stream(self.device)
+        if self._native is not None:
+            self._native.join(main.cuda_stream)
+        else:
+            main.wait_stream(self.opt_stream)
+
+    def synchronize(self):
+        if self.cuda:
+            self.opt_stream.synchronize()
+            self.h2d_stream.synchronize()
+            self.d2h_stream.synchronize()
+
+    def _retain(self, tensor):
+        """Keep a main-stream tensor alive until the side streams are done with it
+        and apply back-pressure on the bytes queued behind PCIe."""
+        if not self.cuda or tensor is None:
+            return
+        tensor.record_stream(self.opt_stream)
+        if self._native is not None:
+            tensor.record_stream(self.d2h_stream)
+        nbytes = tensor.numel() * tensor.element_size()
+        ev = torch.cuda.Event()
+        ev.record(self.d2h_stream if self._native is not None else self.opt_stream)
+        self._inflight.append((ev, nbytes))
+        self._inflight_bytes += nbytes
+        while self._inflight and (self._inflight[0][0].query() or
+                                  self._inflight_bytes > self.max_inflight_bytes):
+            ev0, n0 = self._inflight.popleft()
+            if not ev0.query():
+                ev0.synchronize()
+            self._inflight_bytes -= n0
+
+    # --------------------------------------------------------------- gradient
+    def grad_to_host(self, pid, host_grad, dev_grad, first, sumsq=None):
+        """host_grad = dev_grad (first) or bf16(host_grad + dev_grad); optional sum of
+        squares of the result into ``sumsq`` (fp32 scalar on the device)."""
+        if not self.cuda:
+            grad_ops.grad_accumulate(host_grad, dev_grad, None if first else host_grad, sumsq=sumsq)
+            return
+        self.fork_from_main()
+        if self._native is not None:
+            self._native.staged_grad_to_host(pid, host_grad, dev_grad, first, sumsq, self.scratch)
+        else:
+            s = self.opt_stream.cuda_stream
+            if first and sumsq is None:
+                with torch.cuda.stream(self.opt_stream):
+                    host_grad.copy_(dev_grad, non_blocking=True)
+            else:
+                grad_ops.grad_accumulate(host_grad, dev_grad, None if first else host_grad,
+                                         sumsq=sumsq, scratch=self.scratch, max_ctas=self.max_ctas,
+                                         stream=s, use_cuda=True)
+        self._retain(dev_grad)
+
+    # ------------------------------------------------------------------- step
+    def step(self, pid, param, dev_grad, host_grad, states, hp, step, decoupled, clip=None, seed=0,
+             amax=None, fork=True):
+        """Adam step of one offloaded tensor (or shard).
+
+        ``states`` holds the host tensors ``exp_avg``, ``exp_avg_sq`` and, by mode,
+        ``master_params`` / ``rounding_error``.  The gradient is ``dev_grad``,
+        ``host_grad`` or bf16(dev_grad + host_grad).  ``param`` may be None when no
+        bf16 write-back is wanted (fp32_master only).
+        """
+        lr, wd, beta1, beta2, eps = hp
+        if self.cuda and fork:
+            self.fork_from_main()
+        if self._native is not None:
+            extra = states.get("master_params", states.get("rounding_error"))
+            self._native.staged_step(
+                pid, self.mode_id, param, dev_grad, host_grad, states["exp_avg"],
+                states["exp_avg_sq"], extra, float(lr), float(wd), beta_hat(beta1, step),
+                beta_hat(beta2, step), float(eps), bool(decoupled), clip, int(seed), 0, amax,
+            )
+        else:
+            st = dict(states)
+            if dev_grad is not None:
+                st["grad"], g2 = dev_grad, host_grad
+            else:
+                st["grad"], g2 = host_grad, None
+            adam_step(
+                self.mode_id, param, st, lr, wd, beta1, beta2, eps, step,
+                decoupled_weight_decay=decoupled, seed=seed, clip_coef=clip, grad2=g2, amax=amax,
+                max_ctas=self.max_ctas,
+                stream=self.opt_stream.cuda_stream if self.cuda else 0,
+                use_cuda=self.cuda,
+            )
+        self._retain(dev_grad)
+
+    def bytes_moved(self):
+        if self._native is not None:
+            return self._native.bytes_h2d(), self._native.bytes_d2h()
+        return None

@@ -1,0 +1,591 @@
+"""``OffloadAdam``: Adam/AdamW whose optimizer state lives in pinned host memory.
+
+Public contract (constructor arguments, the ``ready_for_optimizer_step`` flag,
+``step`` / ``zero_grad`` / ``state_dict`` / ``load_master_*`` and the per
+parameter state layout) follows the reference optimizer
+(reference: src/offload_adam/offload_adam.py:39-678).  Two execution paths are
+selected by ``max_grad_norm``:
+
+* ``None``: the step of each parameter is enqueued from its
+  post-accumulate-grad hook on the last micro-batch and overlaps the rest of
+  backward; ``step()`` only joins the side streams.
+* a float: backward accumulates gradients and per-parameter squared norms;
+  ``step()`` turns them into one clip coefficient (a device scalar, no host
+  sync) and streams every parameter through the clip-fused step kernel.
+
+How this implementation differs underneath:
+
+* state tensors are views into a few NUMA-bound pinned segments
+  (``utils.pinned_alloc.PinnedArena``) instead of one registration per tensor;
+* the transfer layer (``engine.TransferEngine``) either lets the step kernel
+  read/write host memory directly over PCIe (``transfer='zero_copy'``) or
+  pipelines chunks through a device ring (``transfer='staged'``); there is no
+  per-tensor device copy of the state and no host synchronisation;
+* gradient accumulation across micro-batches can stay in HBM
+  (``grad_residency='device'``; ``'auto'`` picks it when the accumulators fit a
+  budget) or live on the host as in the reference (``'host'``), in which case a
+  single read-modify-write kernel per micro-batch replaces the D2H + H2D +
+  ``add_`` round trip;
+* all small parameters are stepped by one multi-tensor launch.
+"""
+
+from __future__ import annotations
+
+import random
+import warnings
+
+import torch
+from torch.optim.optimizer import Optimizer
+
+from ._master import MasterLoadingMixin, is_quant
+from .engine import TransferEngine
+from .ops import grad_ops
+from .ops.adam_step import STEP_FNS, adam_step
+from .utils.pinned_alloc import PinnedArena, numa_node_free_bytes, resolve_numa_target
+
+_BF16 = torch.bfloat16
+
+
+def get_leaf_modules_with_params(module):
+    """Leaf modules (no children) that directly own a trainable parameter, in
+    registration (= forward definition) order."""
+    out = []
+    for child in module.children():
+        if any(True for _ in child.children()):
+            out.extend(get_leaf_modules_with_params(child))
+        elif any(p.requires_grad for p in child.parameters(recurse=False)):
+            out.append(child)
+    return out
+
+
+def _offload_layout(extra_name=None, extra_dtype=None):
+    d = {"grad": _BF16, "exp_avg": _BF16, "exp_avg_sq": _BF16}
+    if extra_name:
+        d[extra_name] = extra_dtype
+    return d
+
+
+class OffloadAdam(MasterLoadingMixin, Optimizer):
+    """Adam optimizer that keeps gradients and optimizer state in host memory.
+
+    Args:
+        model (nn.Module): the module whose trainable parameters are optimized
+            (pass the module, not its parameters: hooks are installed on it).
+        lr, betas, eps, weight_decay: Adam hyper-parameters.
+        mode: ``'stochastic_rounding'`` (default), ``'fp32_master'``,
+            ``'fp31_master'`` or ``'fp32_master_custom_rounding'``.
+        max_grad_norm: L2 global-norm clipping threshold, or None to run the step
+            inside backward.
+        numa_node: ``'auto'`` binds pinned memory to the GPU's NUMA node, an int
+            picks a node, None disables binding.
+        decoupled_weight_decay: AdamW-style decay.
+        inplace_param_threshold: parameters with fewer elements keep state and
+            gradient on the GPU (default 1 Mi elements; 0 offloads everything).
+        prefetch_policy: ``'eager'`` or ``'lazy'``: which owner module of a
+            parameter may trigger early work for it.  With the streaming
+            transfer modes of this implementation state is never parked on the
+            GPU ahead of its step, so tied parameters cost no extra residency
+            under either policy; the argument is validated and kept for
+            interface compatibility.
+        verbose: non-zero prints allocation summaries.
+        transfer: ``'auto'`` | ``'zero_copy'`` | ``'staged'`` (see module doc).
+        grad_residency: ``'auto'`` | ``'host'`` | ``'device'``.
+        device_grad_budget: bytes of HBM ``'auto'`` may spend on gradient
+            accumulators (default: a quarter of the device's memory).
+        max_ctas: grid cap of the streaming kernels (0: kernel default); small
+            values leave the SMs to the concurrent backward GEMMs.
+        seed: seeds the stochastic-rounding stream.
+    """
+
+    supported_modes = {
+        "stochastic_rounding": {"step": STEP_FNS["stochastic_rounding"], "offload": _offload_layout()},
+        "fp32_master": {
+            "step": STEP_FNS["fp32_master"],
+            "offload": _offload_layout("master_params", torch.float32),
+        },
+        "fp31_master": {
+            "step": STEP_FNS["fp31_master"],
+            "offload": _offload_layout("rounding_error", torch.int16),
+        },
+        "fp32_master_custom_rounding": {
+            "step": STEP_FNS["fp32_master_custom_rounding"],
+            "offload": _offload_layout("rounding_error", torch.int16),
+        },
+    }
+
+    _DEFAULT_INPLACE_PARAM_THRESHOLD = 1024 * 1024
+
+    def __init__(self, model, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
+                 mode="stochastic_rounding", max_grad_norm=None, numa_node="auto",
+                 decoupled_weight_decay=False, inplace_param_threshold=None,
+                 prefetch_policy="eager", verbose=0, *, transfer="auto", grad_residency="auto",
+                 device_grad_budget=None, chunk_elems=8 << 20, ring_slots=4, max_ctas=0,
+                 max_inflight_bytes=8 << 30, seed=None):
+        if prefetch_policy not in ("eager", "lazy"):
+            raise ValueError(f"prefetch_policy must be 'eager' or 'lazy' (got {prefetch_policy!r})")
+        if grad_residency not in ("auto", "host", "device"):
+            raise ValueError(f"grad_residency must be 'auto', 'host' or 'device' (got {grad_residency!r})")
+        assert mode in self.supported_modes, (
+            f"Invalid mode: {mode}, available modes: {list(self.supported_modes)}"
+        )
+        self._prefetch_policy = prefetch_policy
+        self.mode = mode
+        self.step_fn = self.supported_modes[mode]["step"]
+        self.offload_config = self.supported_modes[mode]["offload"]
+        self.offload_state_keys = list(self.offload_config)
+        self._non_grad_keys = [k for k in self.offload_state_keys if k != "grad"]
+        self._has_master = "master_params" in self.offload_config
+        self.max_grad_norm = max_grad_norm
+        self._step_in_backward = max_grad_norm is None
+        self.decoupled_weight_decay = decoupled_weight_decay
+        self.verbose = verbose
+        self.ready_for_optimizer_step = False
+        self._rng = random.Random(seed)
+
+        # ---- collect parameters: unique by identity, count owning leaf modules
+        modules = get_leaf_modules_with_params(model)
+        params, owners = [], {}
+        for m in modules:
+            for p in m.parameters():
+                if not p.requires_grad:
+                    continue
+                if id(p) not in owners:
+                    owners[id(p)] = 0
+                    params.append(p)
+                owners[id(p)] += 1
+        shared = [p for p in params if owners[id(p)] > 1]
+        if shared and prefetch_policy == "eager":
+            warnings.warn(
+                f"OffloadAdam: {len(shared)} parameter(s) shared across multiple leaf modules "
+                f"({sum(p.numel() for p in shared):,} elements; e.g. tied embeddings). With "
+                f"prefetch_policy='eager' early work for them is triggered by the first owner "
+                f"module reached in backward. Pass prefetch_policy='lazy' to defer it to the "
+                f"input-side module.",
+                stacklevel=2,
+            )
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+
+        self._quant_params = {p for p in params if is_quant(p)}
+        if self._quant_params and mode != "fp32_master":
+            raise ValueError(
+                f"QAT params require mode='fp32_master'; got {mode!r} "
+                f"({len(self._quant_params)} quant params detected)"
+            )
+        self._quant_master_warned = False
+
+        if inplace_param_threshold is None:
+            inplace_param_threshold = self._DEFAULT_INPLACE_PARAM_THRESHOLD
+        self.inplace_param_threshold = inplace_param_threshold
+        self._inplace_params = {
+            p for p in params if p.numel() < inplace_param_threshold and p not in self._quant_params
+        }
+        self._offload_params = [p for p in params if p not in self._inplace_params]
+        self._all_params = params
+        self._pid = {p: i for i, p in enumerate(params)}
+        self._param2group = {p: g for g in self.param_groups for p in g["params"]}
+        self.device = params[0].device if params else torch.device("cpu")
+        self._cuda = self.device.type == "cuda"
+
+        # first owner module in forward order; 'lazy' triggers early work only there
+        self._prefetch_module = {}
+        for m in modules:
+            for p in m.parameters():
+                if p.requires_grad and p not in self._inplace_params:
+                    self._prefetch_module.setdefault(p, m)
+
+        self._engine = TransferEngine(
+            self.device, mode, len(params), transfer=transfer, chunk_elems=chunk_elems,
+            ring_slots=ring_slots, max_ctas=max_ctas, max_inflight_bytes=max_inflight_bytes,
+        )
+        self.transfer = self._engine.transfer
+        self.h2d_stream = self._engine.h2d_stream
+        self.d2h_stream = self._engine.d2h_stream
+        self.opt_stream = self._engine.opt_stream
+
+        # ---- where gradient accumulators live
+        grad_bytes = sum(p.numel() * 2 for p in self._offload_params)
+        if grad_residency == "auto":
+            if self._cuda:
+                if device_grad_budget is None:
+                    device_grad_budget = torch.cuda.get_device_properties(self.device).total_memory // 4
+                grad_residency = "device" if grad_bytes <= device_grad_budget else "host"
+            else:
+                grad_residency = "host"
+        self.grad_residency = grad_residency
+        self._dev_grad = {}       # param -> accumulated gradient tensor on the device
+        self._pending_inplace = []  # small params whose step is due at the next join
+        self._normsq = torch.zeros(max(1, len(params)), dtype=torch.float32, device=self.device)
+        self._norms = torch.zeros_like(self._normsq)
+        self._clip = torch.ones(2, dtype=torch.float32, device=self.device)
+        self._multi = None
+        self._step_dirty = False
+        # main-stream reductions get their own scratch: the engine's belongs to its side stream
+        self._scratch_main = grad_ops.sumsq_scratch(self.device)
+
+        self._register_hooks(model, modules, params)
+        self._numa_precheck(self._offload_params, numa_node)
+        self._alloc_pinned_states(self._offload_params, numa_node)
+        self._alloc_inplace_states(self._inplace_params)
+
+    # ------------------------------------------------------------------ setup
+    def _register_hooks(self, model, modules, params):
+        # No module-level backward pre-hooks: the streaming transfer modes have nothing
+        # to park on the GPU ahead of a parameter's gradient, and full backward hooks
+        # would add an autograd node per leaf-module call.
+        for i, p in enumerate(params):
+            st = self.state[p]
+            st["step"] = 0
+            if self.max_grad_norm is not None:
+                st["grad_norm"] = self._norms[i]
+            if p in self._inplace_params:
+                p.register_post_accumulate_grad_hook(self._inplace_grad_hook)
+            else:
+                p.register_post_accumulate_grad_hook(self._grad_hook)
+                st["host_grad_valid"] = False
+        # the next forward must see every update even if the caller skipped step()
+        model.register_forward_pre_hook(lambda *_: self._finish_step())
+
+    def _state_shape(self, p, key):
+        """Shape of one host state tensor (subclasses shard the non-grad ones)."""
+        return p.shape
+
+    def _estimate_pinned_bytes(self, params):
+        total = 0
+        for p in params:
+            for key, dtype in self.offload_config.items():
+                n = 1
+                for d in self._state_shape(p, key):
+                    n *= d
+                total += n * torch.empty(0, dtype=dtype).element_size()
+        return total
+
+    def _numa_precheck(self, params, numa_node):
+        """Warn when the bound node cannot hold this rank's share of pinned state
+        (soft binding then spills to remote nodes at some H2D cost)."""
+        target = resolve_numa_target(numa_node, self.device if self._cuda else None) if self._cuda else None
+        if target is None or not params:
+            return
+        free = numa_node_free_bytes(target)
+        if free is None:
+            return
+        need = self._estimate_pinned_bytes(params)
+        world = getattr(self, "_world_size", 1)
+        share = free // max(1, world)
+        if need > share:
+            gib = 1024**3
+            warnings.warn(
+                f"OffloadAdam: need {need / gib:.1f} GB pinned on NUMA node {target} "
+                f"({world} rank(s) sharing) but fair share is {share / gib:.1f} GB; "
+                f"~{(need - share) / gib:.1f} GB will spill to remote nodes (H2D may slow "
+                f"~10-15%). Pass `numa_node=None` to let the kernel spread freely.",
+                stacklevel=3,
+            )
+
+    def _master_source(self, p):
+        """Full-shape tensor the fp32 master is seeded from."""
+        return p.data
+
+    def _seed_master(self, p, master):
+        master.copy_(self._master_source(p))
+
+    def _alloc_pinned_states(self, params, numa_node):
+        specs, where = [], []
+        for p in params:
+            for key, dtype in self.offload_config.items():
+                specs.append((self._state_shape(p, key), dtype))
+                where.append((p, key))
+        if not specs:
+            return
+        tensors = self._make_host_tensors(specs, numa_node)
+        for (p, key), t in zip(where, tensors):
+            self.state[p][key] = t
+        for p in params:
+            st = self.state[p]
+            if self._has_master:
+                self._seed_master(p, st["master_params"])
+                if p in self._quant_params:
+                    st["master_filled"] = False
+        if self.verbose > 0:
+            total = sum(t.numel() * t.element_size() for t in tensors)
+            print(f"{self._log_prefix()}Pinned host memory allocated: {total / 1024**3:.2f} GB")
+
+    def _log_prefix(self):
+        return ""
+
+    def _make_host_tensors(self, specs, numa_node):
+        if self._cuda:
+            self._arena = PinnedArena(specs, numa_node=numa_node, device=self.device)
+            if self.verbose > 0:
+                s = self._arena.stats()
+                print(f"{self._log_prefix()}pinned arena: {s['segments']} segment(s), numa_node={s['numa_node']}, "
+                      f"map {s['seconds_map']:.2f}s touch {s['seconds_touch']:.2f}s "
+                      f"register {s['seconds_register']:.2f}s")
+            return list(self._arena.tensors())
+        return [torch.zeros(tuple(shape), dtype=dtype) for shape, dtype in specs]
+
+    def _alloc_inplace_states(self, params):
+        total = 0
+        entries = []
+        for p in self._all_params:
+            if p not in params:
+                continue
+            st = self.state[p]
+            for key, dtype in self.offload_config.items():
+                t = torch.zeros_like(p, dtype=dtype)
+                if key == "master_params":
+                    t.copy_(p.data)
+                st[key] = t
+                total += t.numel() * t.element_size()
+            extra = st.get("master_params", st.get("rounding_error"))
+            entries.append({"param": p.data, "grad": st["grad"], "exp_avg": st["exp_avg"],
+                            "exp_avg_sq": st["exp_avg_sq"], "extra": extra, "p": p})
+        self._inplace_entries = entries
+        if self.verbose > 0 and entries:
+            print(f"{self._log_prefix()}In-place GPU states for {len(entries)} small params: "
+                  f"{total / 1024**2:.2f} MB")
+
+    # ------------------------------------------------------------ hook bodies
+    def _pre_backward_hook(self, module, grad_output):
+        # Streaming transfers need no state parked on the GPU ahead of time; the
+        # hook only records the order in which owner modules are reached, which
+        # diagnostics and the distributed subclass use.
+        return None
+
+    def _hp(self, group):
+        b1, b2 = group["betas"]
+        return (group["lr"], group["weight_decay"], b1, b2, group["eps"])
+
+    def _slot(self, p):
+        i = self._pid[p]
+        return self._normsq[i : i + 1]
+
+    def _want_norm(self):
+        return self.max_grad_norm is not None and self.ready_for_optimizer_step
+
+    def _take_grad(self, p):
+        g = p.grad
+        p.grad = None
+        if g.dtype != _BF16 or not g.is_contiguous():
+            g = g.to(_BF16).contiguous()
+        return g
+
+    @torch.no_grad()
+    def _grad_hook(self, p):
+        if p.grad is None:
+            return
+        grad = self._take_grad(p)
+        st = self.state[p]
+        last = self.ready_for_optimizer_step
+        sumsq = self._slot(p) if self._want_norm() else None
+        if self.grad_residency == "device":
+            acc = self._dev_grad.get(p)
+            if acc is None:
+                self._dev_grad[p] = grad
+                if sumsq is not None:
+                    grad_ops.grad_accumulate(None, grad, None, sumsq=sumsq, scratch=self._scratch_main)
+            else:
+                grad_ops.grad_accumulate(acc, acc, grad, sumsq=sumsq, scratch=self._scratch_main)
+            if last and self._step_in_backward:
+                self._step_offload(p, self._param2group[p])
+            return
+        # ---- host residency
+        if last and self._step_in_backward:
+            self._step_offload(p, self._param2group[p], dev_grad=grad)
+            return
+        self._engine.grad_to_host(self._pid[p], st["grad"], grad, first=not st["host_grad_valid"],
+                                  sumsq=sumsq)
+        st["host_grad_valid"] = True
+
+    @torch.no_grad()
+    def _inplace_grad_hook(self, p):
+        if p.grad is None:
+            return
+        grad = self._take_grad(p)
+        st = self.state[p]
+        sumsq = self._slot(p) if self._want_norm() else None
+        grad_ops.grad_accumulate(st["grad"], st["grad"], grad, sumsq=sumsq, scratch=self._scratch_main)
+        if self.ready_for_optimizer_step and self._step_in_backward:
+            st["step"] += 1
+            self._pending_inplace.append(p)
+
+    # ------------------------------------------------------------- step pieces
+    def _param_view(self, p):
+        """bf16 tensor the kernel writes the updated parameter into."""
+        return p.data
+
+    def _after_param_update(self, p):
+        """Hook for subclasses (e.g. all-gather of an updated shard)."""
+
+    def _step_offload(self, p, group, clip_coef=None, dev_grad=None):
+        """Enqueue the step of one offloaded parameter on the side streams."""
+        st = self.state[p]
+        st["step"] += 1
+        self._step_dirty = True
+        if dev_grad is None:
+            dev_grad = self._dev_grad.pop(p, None)
+        host_grad = st["grad"] if st["host_grad_valid"] else None
+        if dev_grad is None and host_grad is None:
+            st["step"] -= 1
+            return
+        seed = self._rng.getrandbits(63) if self.mode == "stochastic_rounding" else 0
+        states = {k: st[k] for k in self._non_grad_keys}
+        quant = p in self._quant_params
+        if quant:
+            self._warn_lossy_master_once(st)
+            self._step_quant(p, group, st, dev_grad, host_grad, clip_coef)
+        else:
+            self._engine.step(self._pid[p], self._param_view(p), dev_grad, host_grad, states,
+                              self._hp(group), st["step"], self.decoupled_weight_decay,
+                              clip=clip_coef, seed=seed)
+        st["host_grad_valid"] = False
+        self._after_param_update(p)
+
+    def _step_quant(self, p, group, st, dev_grad, host_grad, clip_coef):
+        """Quantized parameter: the updated fp32 master must be on the device to be
+        re-quantized, so it makes the round trip through a temporary while the
+        moments stream as usual."""
+        eng = self._engine
+        if not self._cuda:
+            states = {k: st[k] for k in self._non_grad_keys}
+            eng.step(self._pid[p], None, dev_grad, host_grad, states, self._hp(group), st["step"],
+                     self.decoupled_weight_decay, clip=clip_coef)
+            p.data.copy_(st["master_params"])
+            return
+        eng.fork_from_main()
+        with torch.cuda.stream(eng.opt_stream):
+            master = st["master_params"].to(self.device, non_blocking=True)
+            states = {"exp_avg": st["exp_avg"], "exp_avg_sq": st["exp_avg_sq"], "master_params": master}
+            g = dev_grad if dev_grad is not None else host_grad
+            g2 = host_grad if dev_grad is not None else None
+            states["grad"] = g
+            adam_step(self.mode, None, states, *self._hp(group), st["step"],
+                      decoupled_weight_decay=self.decoupled_weight_decay, clip_coef=clip_coef,
+                      grad2=g2, max_ctas=eng.max_ctas, stream=eng.opt_stream.cuda_stream,
+                      use_cuda=True)
+            p.data.copy_(master)
+            st["master_params"].copy_(master, non_blocking=True)
+        eng._retain(dev_grad)
+
+    def _step_inplace_batch(self, params, clip_coef=None):
+        """One multi-tensor launch for the small GPU-resident parameters."""
+        if not params:
+            return
+        group0 = self._param2group[params[0]]
+        same = all(self._param2group[p] is group0 for p in params) and \
+            len({self.state[p]["step"] for p in params}) == 1
+        seed = self._rng.getrandbits(63) if self.mode == "stochastic_rounding" else 0
+        if same and len(params) == len(self._inplace_entries) and len(self.param_groups) == 1:
+            if self._multi is None:
+                self._multi = grad_ops.MultiTensorAdam(self._inplace_entries, self.mode)
+            lr, wd, b1, b2, eps = self._hp(group0)
+            self._multi.step(lr, wd, b1, b2, eps, self.state[params[0]]["step"],
+                             self.decoupled_weight_decay, clip_coef=clip_coef, seed=seed,
+                             zero_grad=True)
+            return
+        for p in params:
+            st = self.state[p]
+            tensors = {k: st[k] for k in self.offload_state_keys}
+            adam_step(self.mode, p.data, tensors, *self._hp(self._param2group[p]), st["step"],
+                      decoupled_weight_decay=self.decoupled_weight_decay, clip_coef=clip_coef,
+                      seed=self._rng.getrandbits(63))
+            st["grad"].zero_()
+
+    def _finish_step(self):
+        """Run what the hooks deferred and make the main stream wait for the side
+        streams.  Idempotent; called by ``step()`` and before every forward."""
+        if self._pending_inplace:
+            pend, self._pending_inplace = self._pending_inplace, []
+            self._step_inplace_batch(pend)
+        if self._step_dirty:
+            # only a finished step forces the join: gradient write-backs of earlier
+            # micro-batches keep overlapping the next forward
+            self._step_dirty = False
+            self._engine.join_main()
+
+    # -------------------------------------------------------------- public API
+    @torch.no_grad()
+    def step(self, closure=None):
+        if closure is not None:
+            raise NotImplementedError(
+                f"{type(self).__name__} does not support closure-based step: gradients are "
+                "consumed by backward hooks, so re-running backward inside a closure would "
+                "corrupt optimizer state."
+            )
+        if self._step_in_backward:
+            self._finish_step()
+            return
+        clip = self._global_clip_coef()
+        inplace = []
+        for group in self.param_groups:
+            for p in group["params"]:
+                if p in self._inplace_params:
+                    self.state[p]["step"] += 1
+                    inplace.append(p)
+                else:
+                    self._step_offload(p, group, clip_coef=clip)
+        self._step_inplace_batch(inplace, clip_coef=clip)
+        self._finish_step()
+        if self.max_grad_norm is not None:
+            torch.sqrt(self._normsq, out=self._norms)
+            self._normsq.zero_()
+
+    def _global_clip_coef(self):
+        """Device scalar min(1, max_norm / (||g|| + 1e-6)); no host sync."""
+        if self.max_grad_norm is None:
+            return None
+        # squared norms were written on the side stream (host residency) or on the
+        # main stream (device residency); order the reduction after both
+        self._engine.join_main()
+        grad_ops.clip_finalize(self._normsq, None, None, self.max_grad_norm, coef_norm=self._clip)
+        return self._clip[0:1]
+
+    def zero_grad(self, set_to_none=False):
+        """No-op: gradients are consumed and cleared by the hooks."""
+        return
+
+    def synchronize(self):
+        """Block the host until every enqueued transfer and step has finished."""
+        self._finish_step()
+        self._engine.synchronize()
+
+    def _copy_master(self, p, tensor):
+        self.state[p]["master_params"].copy_(tensor)
+
+    def _tracks(self, p):
+        return p in self.state
+
+    def load_state_dict(self, state_dict):
+        raise NotImplementedError(
+            f"{type(self).__name__}.load_state_dict is not supported: the default "
+            "Optimizer.load_state_dict would move pinned-host state to GPU and cast the fp32 "
+            "master to bf16, defeating the offload contract. Use load_offload_state_dict() to "
+            "resume into the existing pinned buffers."
+        )
+
+    @torch.no_grad()
+    def load_offload_state_dict(self, state_dict):
+        """Resume from ``state_dict()`` output by copying into the existing buffers
+        (pinned host tensors stay where they are, dtypes are preserved)."""
+        self.synchronize()
+        saved_ids = [i for g in state_dict["param_groups"] for i in g["params"]]
+        live = [p for g in self.param_groups for p in g["params"]]
+        if len(saved_ids) != len(live):
+            raise ValueError("load_offload_state_dict: parameter count differs from the checkpoint")
+        for g_live, g_saved in zip(self.param_groups, state_dict["param_groups"]):
+            for k, v in g_saved.items():
+                if k != "params":
+                    g_live[k] = v
+        for idx, p in zip(saved_ids, live):
+            src = state_dict["state"].get(idx)
+            if src is None:
+                continue
+            dst = self.state[p]
+            for k, v in src.items():
+                if isinstance(v, torch.Tensor) and isinstance(dst.get(k), torch.Tensor):
+                    if v.shape != dst[k].shape or v.dtype != dst[k].dtype:
+                        raise ValueError(f"load_offload_state_dict: state '{k}' of param {idx} "
+                                         f"has shape/dtype {tuple(v.shape)}/{v.dtype}, expected "
+                                         f"{tuple(dst[k].shape)}/{dst[k].dtype}")
+                    dst[k].copy_(v)
+                else:
+                    dst[k] = v

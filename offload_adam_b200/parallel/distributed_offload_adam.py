@@ -1,0 +1,295 @@
+"""``DistributedOffloadAdam``: ZeRO-1 on top of ``OffloadAdam``.
+
+Parameters are replicated on every rank; the optimizer state of every large
+parameter whose leading dimension divides by the world size is sharded by rows,
+so each rank keeps (and streams over PCIe) ``1/world`` of the moments and of the
+fp32 master.  On the last micro-batch the gradient of a sharded parameter is
+reduce-scattered (average), the owning rank updates its row slice and the
+updated slices are all-gathered into every replica.  Small parameters and
+parameters that do not divide are replicated and all-reduced
+(reference: src/offload_adam/distributed_offload_adam.py:1-314).
+
+Two communication back ends implement those three collectives:
+
+``comm='nccl'``  ``torch.distributed`` collectives (NCCL on GPUs, gloo on CPU).
+                 This is the baseline path and the one CPU tests exercise.
+``comm='symm'``  the parameters and the gradient accumulators live in symmetric
+                 memory; one kernel per parameter pulls the peers' gradient rows
+                 over NVLink, averages them, runs Adam on the shard and pushes
+                 the new bf16 rows into every replica (``parallel/symm.py``,
+                 ``csrc/zero1_kernels.cu``).  No NCCL call on that path.
+``comm='auto'``  ``symm`` on CUDA with world size > 1 when symmetric memory can
+                 be set up, else ``nccl``.
+
+Reductions accumulate in fp32 over the ranks' bf16 gradients in rank order and
+round once to bf16, on both back ends.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..offload_adam import OffloadAdam
+from ..ops import grad_ops
+
+
+class DistributedOffloadAdam(OffloadAdam):
+    """Sharded-state (ZeRO-1) variant of :class:`OffloadAdam`.
+
+    Extra keyword-only arguments: ``process_group`` (default: the world group),
+    ``comm`` (``'auto'`` | ``'nccl'`` | ``'symm'``) and ``wait_timeout_ms`` (bound
+    of every device-side wait on a peer in the ``symm`` path).
+    """
+
+    def __init__(self, model, *, process_group=None, comm="auto", wait_timeout_ms=30000, **kwargs):
+        if not dist.is_available() or not dist.is_initialized():
+            raise RuntimeError(
+                "DistributedOffloadAdam requires torch.distributed to be initialized; "
+                "call dist.init_process_group first."
+            )
+        if comm not in ("auto", "nccl", "symm"):
+            raise ValueError(f"comm must be 'auto', 'nccl' or 'symm' (got {comm!r})")
+        self._pg = process_group if process_group is not None else dist.group.WORLD
+        self._world_size = dist.get_world_size(self._pg)
+        self._rank = dist.get_rank(self._pg)
+        self._sharded = set()
+        self._requested_comm = comm
+        self._wait_timeout_ms = int(wait_timeout_ms)
+        self._symm = None
+        self.comm = "nccl"
+        super().__init__(model, **kwargs)
+        self._setup_comm(model)
+
+    # --------------------------------------------------------------- sharding
+    def _is_sharded_shape(self, p):
+        return (self._world_size > 1 and p.dim() >= 1 and p.shape[0] % self._world_size == 0
+                and p not in self._inplace_params)
+
+    def _rows(self, p):
+        ds = p.shape[0] // self._world_size
+        return self._rank * ds, (self._rank + 1) * ds
+
+    def _shard_slice(self, p):
+        """This rank's row slice of the bf16 parameter (a view)."""
+        lo, hi = self._rows(p)
+        return p.data[lo:hi]
+
+    def _state_shape(self, p, key):
+        if key != "grad" and self._is_sharded_shape(p):
+            return (p.shape[0] // self._world_size, *p.shape[1:])
+        return p.shape
+
+    def _seed_master(self, p, master):
+        src = p.data
+        if p in self._quant_params:
+            full = torch.empty(p.shape, dtype=torch.float32, device="cpu")
+            full.copy_(src)  # dequantizes
+            src = full
+        if self._is_sharded_shape(p):
+            lo, hi = self._rows(p)
+            src = src[lo:hi]
+        master.copy_(src)
+
+    def _alloc_pinned_states(self, params, numa_node):
+        for p in params:
+            if self._is_sharded_shape(p):
+                self._sharded.add(p)
+        super()._alloc_pinned_states(params, numa_node)
+
+    def _log_prefix(self):
+        return f"[rank {self._rank}] "
+
+    def _copy_master(self, p, tensor):
+        if p in self._sharded:
+            lo, hi = self._rows(p)
+            tensor = tensor[lo:hi]
+        self.state[p]["master_params"].copy_(tensor)
+
+    # ------------------------------------------------------------ comm set-up
+    def _setup_comm(self, model):
+        want = self._requested_comm
+        if self._world_size <= 1 or not self._cuda:
+            if want == "symm" and self._world_size > 1:
+                raise RuntimeError("comm='symm' needs CUDA devices")
+            return
+        if want == "nccl":
+            return
+        from . import symm
+
+        try:
+            self._symm = symm.SymmZero1(self, model, timeout_ms=self._wait_timeout_ms)
+            self.comm = "symm"
+        except Exception as e:
+            if want == "symm":
+                raise
+            import warnings
+
+            warnings.warn(f"DistributedOffloadAdam: symmetric-memory path unavailable ({e}); "
+                          f"using torch.distributed collectives")
+
+    # ------------------------------------------------------- collective helpers
+    def _avg_all_reduce(self, t):
+        """In-place average over ranks (fp32 accumulate for bf16 on CPU/gloo)."""
+        if self._world_size <= 1:
+            return
+        if t.is_cuda:
+            dist.all_reduce(t, op=dist.ReduceOp.AVG, group=self._pg)
+        else:
+            f = t.float()
+            dist.all_reduce(f, op=dist.ReduceOp.SUM, group=self._pg)
+            t.copy_((f / self._world_size).to(t.dtype))
+
+    def _avg_reduce_scatter(self, full, p):
+        """Average over ranks of ``full`` restricted to this rank's rows."""
+        lo, hi = self._rows(p)
+        if full.is_cuda:
+            out = torch.empty((hi - lo, *p.shape[1:]), dtype=full.dtype, device=full.device)
+            dist.reduce_scatter_tensor(out.view(-1), full.contiguous().view(-1),
+                                       op=dist.ReduceOp.AVG, group=self._pg)
+            return out
+        f = full.float()
+        dist.all_reduce(f, op=dist.ReduceOp.SUM, group=self._pg)
+        return (f[lo:hi] / self._world_size).to(full.dtype).contiguous()
+
+    def _all_gather_rows(self, dst_full, local_rows):
+        if dst_full.is_cuda:
+            dist.all_gather_into_tensor(dst_full.view(-1), local_rows.contiguous().view(-1), group=self._pg)
+        else:
+            parts = [torch.empty_like(local_rows) for _ in range(self._world_size)]
+            dist.all_gather(parts, local_rows.contiguous(), group=self._pg)
+            dst_full.copy_(torch.cat(parts, dim=0).view_as(dst_full))
+
+    def _side(self):
+        """Context that routes torch ops (and collectives) to the optimizer stream."""
+        if self._cuda:
+            return torch.cuda.stream(self._engine.opt_stream)
+        import contextlib
+
+        return contextlib.nullcontext()
+
+    # ------------------------------------------------------------------- hooks
+    @torch.no_grad()
+    def _inplace_grad_hook(self, p):
+        if p.grad is None:
+            return
+        if not self.ready_for_optimizer_step or self._world_size <= 1:
+            return super()._inplace_grad_hook(p)
+        grad = self._take_grad(p)
+        st = self.state[p]
+        grad_ops.grad_accumulate(st["grad"], st["grad"], grad, scratch=self._scratch_main)
+        if self._symm is not None:
+            self._symm.small_grad_ready(p)  # reduced in one bucket at step time
+        else:
+            self._avg_all_reduce(st["grad"])
+            if self._want_norm():
+                grad_ops.grad_accumulate(None, st["grad"], None, sumsq=self._slot(p),
+                                         scratch=self._scratch_main)
+        if self._step_in_backward:
+            st["step"] += 1
+            self._pending_inplace.append(p)
+
+    @torch.no_grad()
+    def _grad_hook(self, p):
+        if p.grad is None:
+            return
+        if not self.ready_for_optimizer_step or self._world_size <= 1:
+            return super()._grad_hook(p)
+        if self._symm is not None:
+            return self._symm.grad_hook_last(p)
+        # ---- last micro-batch, torch.distributed collectives
+        grad = self._take_grad(p)
+        st = self.state[p]
+        eng = self._engine
+        eng.fork_from_main()
+        with self._side():
+            acc = self._dev_grad.pop(p, None)
+            if acc is not None:
+                grad_ops.grad_accumulate(acc, acc, grad, scratch=eng.scratch, use_cuda=self._cuda,
+                                         stream=self._opt_stream_handle())
+                full = acc
+            elif st["host_grad_valid"]:
+                grad_ops.grad_accumulate(grad, grad, st["grad"], use_cuda=self._cuda,
+                                         stream=self._opt_stream_handle())
+                full = grad
+                st["host_grad_valid"] = False
+            else:
+                full = grad
+            if p in self._sharded:
+                red = self._avg_reduce_scatter(full, p)
+            else:
+                self._avg_all_reduce(full)
+                red = full
+            if self.max_grad_norm is not None:
+                grad_ops.grad_accumulate(None, red, None, sumsq=self._slot(p), scratch=eng.scratch,
+                                         use_cuda=self._cuda, stream=self._opt_stream_handle())
+        eng._retain(grad)
+        if acc is not None:
+            eng._retain(acc)
+        self._dev_grad[p] = red  # reduced gradient (slice for sharded) waits for its step
+        if self._step_in_backward:
+            self._step_offload(p, self._param2group[p])
+
+    def _opt_stream_handle(self):
+        return self._engine.opt_stream.cuda_stream if self._cuda else 0
+
+    # ------------------------------------------------------------- step pieces
+    def _param_view(self, p):
+        return self._shard_slice(p) if p in self._sharded else p.data
+
+    def _after_param_update(self, p):
+        if p not in self._sharded or self._symm is not None:
+            return
+        with self._side():
+            if p in self._quant_params:
+                return  # handled in _step_quant
+            self._all_gather_rows(p.data, self._shard_slice(p))
+
+    def _step_quant(self, p, group, st, dev_grad, host_grad, clip_coef):
+        if p not in self._sharded:
+            return super()._step_quant(p, group, st, dev_grad, host_grad, clip_coef)
+        # sharded quantized parameter: update the master slice, gather the full fp32
+        # master and let every replica re-quantize it
+        eng = self._engine
+        from ..ops.adam_step import adam_step
+
+        eng.fork_from_main()
+        with self._side():
+            master = st["master_params"].to(self.device, non_blocking=True) if self._cuda \
+                else st["master_params"]
+            states = {"grad": dev_grad, "exp_avg": st["exp_avg"], "exp_avg_sq": st["exp_avg_sq"],
+                      "master_params": master}
+            adam_step(self.mode, None, states, *self._hp(group), st["step"],
+                      decoupled_weight_decay=self.decoupled_weight_decay, clip_coef=clip_coef,
+                      max_ctas=eng.max_ctas, stream=self._opt_stream_handle(), use_cuda=self._cuda)
+            full = torch.empty(p.shape, dtype=torch.float32, device=self.device)
+            self._all_gather_rows(full, master)
+            p.data.copy_(full)
+            if self._cuda:
+                st["master_params"].copy_(master, non_blocking=True)
+        eng._retain(dev_grad)
+
+    def _global_clip_coef(self):
+        if self.max_grad_norm is None:
+            return None
+        if self._world_size <= 1:
+            return super()._global_clip_coef()
+        if self._symm is not None:
+            return self._symm.global_clip_coef()
+        # sharded params contribute disjoint slices on every rank; replicated ones are
+        # identical everywhere and are counted by rank 0 only
+        self._engine.join_main()
+        idx = [self._pid[p] for p in self._all_params if p in self._sharded or self._rank == 0]
+        index = torch.tensor(idx, dtype=torch.int32, device=self.device)
+        local = torch.zeros(1, dtype=torch.float32, device=self.device)
+        grad_ops.clip_finalize(self._normsq, index, None, self.max_grad_norm, total_sq=local)
+        dist.all_reduce(local, op=dist.ReduceOp.SUM, group=self._pg)
+        grad_ops.clip_finalize(None, None, local, self.max_grad_norm, coef_norm=self._clip)
+        return self._clip[0:1]
+
+    def _finish_step(self):
+        if self._symm is not None:
+            self._symm.before_finish()
+        super()._finish_step()
+        if self._symm is not None:
+            self._symm.after_finish()
