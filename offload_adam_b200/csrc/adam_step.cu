@@ -10,10 +10,12 @@
 //     accumulated host gradient never has to be materialised on the device;
 //   * an optional running max of |master| feeds the NVFP4 tensor scale.
 //
-// The kernel is a grid-stride stream over 16-byte vectors (8 elements).  Each
-// thread issues all loads of two vectors before touching either, which keeps
-// >= 10 independent 16-byte requests in flight per thread; that is what both
-// HBM3e and a PCIe link (when operands are mapped host memory) need to stay busy.
+// The kernel is a grid-stride stream over groups of 16 elements.  Every operand
+// moves with Blackwell's 256-bit global loads/stores (one 32-byte request per
+// bf16 stream, two for the fp32 master), all issued before the first use, so a
+// thread keeps 160-224 bytes in flight and a warp request always covers whole,
+// contiguous 1 KiB runs; that is what both HBM3e and a PCIe link (when operands
+// are mapped host memory) need to stay busy.
 #include "adam_math.cuh"
 #include "adam_step.h"
 
@@ -24,7 +26,7 @@ unsigned long long g_launch_count = 0;
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kUnroll = 2;
+constexpr int kVec = 16;  // elements per thread per iteration (one 32-byte bf16 vector)
 
 struct Ptrs {
   uint16_t* p;
@@ -37,42 +39,24 @@ struct Ptrs {
 
 template <int MODE>
 struct VecRegs {
-  uint4 p, g, g2, m, v, e0, e1;
+  V8 p, g, g2, m, v, e0, e1;
 };
 
 template <int MODE, bool HAS_G2>
 __device__ __forceinline__ void load_vec(VecRegs<MODE>& r, const Ptrs& t, int64_t vec) {
-  const int64_t e = vec * 8;
-  if (MODE != kModeFP32Master) r.p = ld16(t.p + e);  // params stay cacheable (forward re-reads)
-  r.g = ld16_stream(t.g + e);
-  if (HAS_G2) r.g2 = ld16_stream(t.g2 + e);
-  r.m = ld16_stream(t.m + e);
-  r.v = ld16_stream(t.v + e);
+  const int64_t e = vec * kVec;
+  if (MODE != kModeFP32Master) r.p = ld32(t.p + e);  // params stay cacheable (forward re-reads)
+  r.g = ld32_stream(t.g + e);
+  if (HAS_G2) r.g2 = ld32_stream(t.g2 + e);
+  r.m = ld32_stream(t.m + e);
+  r.v = ld32_stream(t.v + e);
   if (MODE == kModeFP32Master) {
     const float* mp = reinterpret_cast<const float*>(t.extra) + e;
-    r.e0 = ld16_stream(mp);
-    r.e1 = ld16_stream(mp + 4);
+    r.e0 = ld32_stream(mp);
+    r.e1 = ld32_stream(mp + 8);
   } else if (MODE == kModeFP31 || MODE == kModeCustom) {
-    r.e0 = ld16_stream(reinterpret_cast<const int16_t*>(t.extra) + e);
+    r.e0 = ld32_stream(reinterpret_cast<const int16_t*>(t.extra) + e);
   }
-}
-
-__device__ __forceinline__ uint32_t half_of(const uint4& q, int j) {
-  uint32_t w = (j < 2) ? q.x : (j < 4) ? q.y : (j < 6) ? q.z : q.w;
-  return (w >> (16 * (j & 1))) & 0xffffu;
-}
-__device__ __forceinline__ void set_half(uint4& q, int j, uint32_t h) {
-  uint32_t* w = (j < 2) ? &q.x : (j < 4) ? &q.y : (j < 6) ? &q.z : &q.w;
-  if (j & 1)
-    *w = (*w & 0x0000ffffu) | (h << 16);
-  else
-    *w = (*w & 0xffff0000u) | (h & 0xffffu);
-}
-__device__ __forceinline__ uint32_t word_of(const uint4& q, int j) {
-  return j == 0 ? q.x : j == 1 ? q.y : j == 2 ? q.z : q.w;
-}
-__device__ __forceinline__ void set_word(uint4& q, int j, uint32_t w) {
-  if (j == 0) q.x = w; else if (j == 1) q.y = w; else if (j == 2) q.z = w; else q.w = w;
 }
 
 // One element.  p16/e16/master are in/out depending on MODE.
@@ -115,20 +99,24 @@ template <int MODE, bool DECOUPLED, bool HAS_G2>
 __device__ __forceinline__ float compute_store_vec(VecRegs<MODE>& r, const Ptrs& t, int64_t vec,
                                                    float clip, const AdamScalars& s,
                                                    uint64_t seed, int64_t elem_offset) {
-  const int64_t e = vec * 8;
-  Philox4 rnd{0, 0, 0, 0};
-  if (MODE == kModeSR) rnd = philox4x32_10((uint64_t)((elem_offset + e) >> 3), seed);
-  uint4 pout = r.p;
+  const int64_t e = vec * kVec;
+  Philox4 rnd[2];
+  if (MODE == kModeSR) {
+    const uint64_t c = (uint64_t)((elem_offset + e) >> 3);
+    rnd[0] = philox4x32_10(c, seed);
+    rnd[1] = philox4x32_10(c + 1, seed);
+  }
+  V8 pout = r.p;
   float amax = 0.f;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < kVec; ++j) {
     uint32_t p16 = (MODE != kModeFP32Master) ? half_of(r.p, j) : 0u;
     uint32_t m16 = half_of(r.m, j), v16 = half_of(r.v, j);
     float master = 0.f;
     int16_t err = 0;
-    if (MODE == kModeFP32Master) master = __uint_as_float(word_of(j < 4 ? r.e0 : r.e1, j & 3));
+    if (MODE == kModeFP32Master) master = __uint_as_float(j < 8 ? r.e0.w[j & 7] : r.e1.w[j & 7]);
     if (MODE == kModeFP31 || MODE == kModeCustom) err = (int16_t)half_of(r.e0, j);
-    uint32_t rand16 = (MODE == kModeSR) ? philox_word16(rnd, j) : 0u;
+    uint32_t rand16 = (MODE == kModeSR) ? philox_word16(rnd[j >> 3], j & 7) : 0u;
     float pf = element_step<MODE, DECOUPLED>(p16, half_of(r.g, j), HAS_G2,
                                              HAS_G2 ? half_of(r.g2, j) : 0u, m16, v16, master,
                                              err, clip, s, rand16);
@@ -136,23 +124,25 @@ __device__ __forceinline__ float compute_store_vec(VecRegs<MODE>& r, const Ptrs&
     set_half(pout, j, p16);
     set_half(r.m, j, m16);
     set_half(r.v, j, v16);
-    if (MODE == kModeFP32Master) set_word(j < 4 ? r.e0 : r.e1, j & 3, __float_as_uint(master));
+    if (MODE == kModeFP32Master) {
+      if (j < 8) r.e0.w[j & 7] = __float_as_uint(master); else r.e1.w[j & 7] = __float_as_uint(master);
+    }
     if (MODE == kModeFP31 || MODE == kModeCustom) set_half(r.e0, j, (uint32_t)(uint16_t)err);
   }
-  if (t.p != nullptr) st16(t.p + e, pout);
-  st16_stream(t.m + e, r.m);
-  st16_stream(t.v + e, r.v);
+  if (t.p != nullptr) st32(t.p + e, pout);
+  st32_stream(t.m + e, r.m);
+  st32_stream(t.v + e, r.v);
   if (MODE == kModeFP32Master) {
     float* mp = reinterpret_cast<float*>(t.extra) + e;
-    st16_stream(mp, r.e0);
-    st16_stream(mp + 4, r.e1);
+    st32_stream(mp, r.e0);
+    st32_stream(mp + 8, r.e1);
   } else if (MODE == kModeFP31 || MODE == kModeCustom) {
-    st16_stream(reinterpret_cast<int16_t*>(t.extra) + e, r.e0);
+    st32_stream(reinterpret_cast<int16_t*>(t.extra) + e, r.e0);
   }
   return amax;
 }
 
-// Scalar path: tails and tensors whose pointers are not 16-byte aligned.
+// Scalar path: tails and tensors whose pointers are not 32-byte aligned.
 template <int MODE, bool DECOUPLED>
 __device__ __forceinline__ float scalar_element(const Ptrs& t, int64_t i, bool has_g2, float clip,
                                                 const AdamScalars& s, uint64_t seed,
@@ -190,23 +180,13 @@ adam_step_kernel(Ptrs t, int64_t n, AdamScalars s, const float* __restrict__ cli
   const int64_t nthreads = (int64_t)gridDim.x * kThreads;
   int64_t scalar_begin = 0;
   if (vector_ok) {
-    const int64_t nvec = n >> 3;
-    scalar_begin = nvec << 3;
-    // each thread walks pairs of vectors: {i, i + nthreads}
-    for (int64_t base = tid; base < nvec; base += nthreads * kUnroll) {
-      VecRegs<MODE> r[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        int64_t vec = base + u * nthreads;
-        if (vec < nvec) load_vec<MODE, HAS_G2>(r[u], t, vec);
-      }
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        int64_t vec = base + u * nthreads;
-        if (vec < nvec)
-          amax = fmaxf(amax, compute_store_vec<MODE, DECOUPLED, HAS_G2>(r[u], t, vec, clip, s, seed,
-                                                                        elem_offset));
-      }
+    const int64_t nvec = n / kVec;
+    scalar_begin = nvec * kVec;
+    for (int64_t vec = tid; vec < nvec; vec += nthreads) {
+      VecRegs<MODE> r;
+      load_vec<MODE, HAS_G2>(r, t, vec);
+      amax = fmaxf(amax, compute_store_vec<MODE, DECOUPLED, HAS_G2>(r, t, vec, clip, s, seed,
+                                                                    elem_offset));
     }
   }
   for (int64_t i = scalar_begin + tid; i < n; i += nthreads)
@@ -248,11 +228,11 @@ cudaError_t launch_adam_step(const AdamStepArgs& a, cudaStream_t stream) {
   s.one_m_b1h = 1.0f - a.beta1_hat;
   s.one_m_b2h = 1.0f - a.beta2_hat;
   s.eps = a.eps;
-  auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 31u) == 0; };
   int vector_ok = al(a.p) && al(a.g) && al(a.g2) && al(a.m) && al(a.v) && al(a.extra) &&
                   ((a.elem_offset & 7) == 0);
-  const int64_t nvec = (a.n + 7) / 8;
-  int64_t want = (nvec + (int64_t)kThreads * kUnroll - 1) / ((int64_t)kThreads * kUnroll);
+  const int64_t nvec = (a.n + kVec - 1) / kVec;
+  int64_t want = (nvec + kThreads - 1) / kThreads;
   int cap = a.max_ctas > 0 ? a.max_ctas : kNumSMs * 8;
   int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
   count_launch();

@@ -47,8 +47,8 @@ __device__ __forceinline__ uint32_t f32_to_bf16_sr_bits(float f, uint32_t rand16
 
 // ----------------------------------------------------------------------------
 // Philox4x32-10: counter = (ctr_lo, ctr_hi, 0, 0), key = (seed_lo, seed_hi).
-// One call yields 128 random bits = eight 16-bit words, enough for one 8-wide
-// bf16 vector.  The CPU restatement in ops/oracle.py generates the same stream.
+// One call yields 128 random bits = eight 16-bit words, i.e. the words of eight
+// consecutive elements.  The CPU restatement in ops/oracle.py generates the same stream.
 // ----------------------------------------------------------------------------
 struct Philox4 {
   uint32_t x, y, z, w;
@@ -77,30 +77,51 @@ __host__ __device__ __forceinline__ Philox4 philox4x32_10(uint64_t counter, uint
 }
 
 // ----------------------------------------------------------------------------
-// 16-byte vector I/O.  The *_stream variants carry cache hints for data touched
-// exactly once (optimizer state): they bypass L1 allocation.
+// 32-byte vector I/O (Blackwell 256-bit global loads/stores): one instruction
+// moves 16 bf16 or 8 fp32 values per thread, so a warp touches 1 KiB of
+// contiguous memory per request.  The *_stream variants are for data touched
+// exactly once (optimizer state, gradients): no L1 allocation, evict-first in L2.
+// Addresses must be 32-byte aligned.
 // ----------------------------------------------------------------------------
-__device__ __forceinline__ uint4 ld16(const void* p) {
-  return *reinterpret_cast<const uint4*>(p);
-}
-__device__ __forceinline__ void st16(void* p, uint4 v) {
-  *reinterpret_cast<uint4*>(p) = v;
-}
-__device__ __forceinline__ uint4 ld16_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+struct V8 {
+  uint32_t w[8];
+};
+__device__ __forceinline__ V8 ld32(const void* p) {
+  V8 v;
+  asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]),
+                 "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7])
                : "l"(p));
   return v;
 }
-__device__ __forceinline__ void st16_stream(void* p, uint4 v) {
-  asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x),
-               "r"(v.y), "r"(v.z), "r"(v.w)
+__device__ __forceinline__ V8 ld32_stream(const void* p) {
+  V8 v;
+  asm volatile(
+      "ld.global.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]),
+        "=r"(v.w[6]), "=r"(v.w[7])
+      : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st32(void* p, const V8& v) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.w[0]),
+               "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]), "r"(v.w[4]), "r"(v.w[5]), "r"(v.w[6]),
+               "r"(v.w[7])
                : "memory");
 }
-
-__device__ __forceinline__ bool aligned16(const void* p) {
-  return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+__device__ __forceinline__ void st32_stream(void* p, const V8& v) {
+  asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p),
+               "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]), "r"(v.w[4]), "r"(v.w[5]),
+               "r"(v.w[6]), "r"(v.w[7])
+               : "memory");
+}
+// j-th 16-bit half of a 16 x bf16 vector
+__device__ __forceinline__ uint32_t half_of(const V8& q, int j) {
+  return (q.w[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+}
+__device__ __forceinline__ void set_half(V8& q, int j, uint32_t h) {
+  uint32_t& w = q.w[j >> 1];
+  w = (j & 1) ? ((w & 0x0000ffffu) | (h << 16)) : ((w & 0xffff0000u) | (h & 0xffffu));
 }
 
 // block-wide sum in a fixed tree order (deterministic for a given blockDim).

@@ -37,32 +37,29 @@ grad_accumulate_kernel(uint16_t* out, const uint16_t* a, const uint16_t* b, int6
   const int64_t nthreads = (int64_t)gridDim.x * kThreads;
   int64_t scalar_begin = 0;
   if (vector_ok) {
-    const int64_t nvec = n >> 3;
-    scalar_begin = nvec << 3;
+    const int64_t nvec = n >> 4;
+    scalar_begin = nvec << 4;
     for (int64_t base = tid; base < nvec; base += 2 * nthreads) {
-      uint4 ra[2], rb[2];
+      V8 ra[2], rb[2];
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         int64_t vec = base + u * nthreads;
         if (vec < nvec) {
-          ra[u] = ld16_stream(a + vec * 8);
-          if (HAS_B) rb[u] = ld16_stream(b + vec * 8);
+          ra[u] = ld32_stream(a + vec * 16);
+          if (HAS_B) rb[u] = ld32_stream(b + vec * 16);
         }
       }
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         int64_t vec = base + u * nthreads;
         if (vec < nvec) {
-          uint4 r = ra[u];
-          if (HAS_B) {
-            r.x = add_pair(r.x, rb[u].x); r.y = add_pair(r.y, rb[u].y);
-            r.z = add_pair(r.z, rb[u].z); r.w = add_pair(r.w, rb[u].w);
+          V8 r = ra[u];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (HAS_B) r.w[j] = add_pair(r.w[j], rb[u].w[j]);
+            if (SUMSQ) acc = sq_acc_pair(r.w[j], acc);
           }
-          if (SUMSQ) {
-            acc = sq_acc_pair(r.x, acc); acc = sq_acc_pair(r.y, acc);
-            acc = sq_acc_pair(r.z, acc); acc = sq_acc_pair(r.w, acc);
-          }
-          if (STORE) st16_stream(out + vec * 8, r);
+          if (STORE) st32_stream(out + vec * 16, r);
         }
       }
     }
@@ -127,9 +124,9 @@ cudaError_t launch_grad_accumulate(const AccumArgs& a, cudaStream_t stream) {
     return cudaSuccess;
   }
   if (a.sumsq_out && !a.scratch) return cudaErrorInvalidValue;
-  auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 31u) == 0; };
   int vector_ok = al(a.out) && al(a.a) && al(a.b);
-  const int64_t nvec = (a.n + 7) / 8;
+  const int64_t nvec = (a.n + 15) / 16;
   int64_t want = (nvec + kThreads * 2 - 1) / (kThreads * 2);
   int cap = a.max_ctas > 0 ? (a.max_ctas < kMaxPartials ? a.max_ctas : kMaxPartials) : kMaxPartials;
   int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));

@@ -137,6 +137,14 @@ def _f32(x, device):
     return torch.tensor(float(x), dtype=torch.float32, device=device)
 
 
+def _sqrt_rn(x: torch.Tensor) -> torch.Tensor:
+    """Correctly rounded fp32 square root.  PyTorch's vectorised CPU sqrt is not
+    always correctly rounded; numpy's is, and so is the CUDA one."""
+    if x.device.type == "cpu":
+        return torch.from_numpy(np.asarray(np.sqrt(x.contiguous().numpy()), dtype=np.float32)).reshape(x.shape)
+    return torch.sqrt(x)
+
+
 @torch.no_grad()
 def adam_step(
     mode,
@@ -186,7 +194,7 @@ def adam_step(
         gf = gf + wd32 * pf
     mf = mf + c1 * (gf - mf)
     vf = vf + c2 * (gf * gf - vf)
-    denom = torch.sqrt(vf) + eps32
+    denom = _sqrt_rn(vf) + eps32
     pf = pf - (lr32 * mf) / denom
 
     m.reshape(-1).copy_(mf.to(torch.bfloat16))
@@ -225,6 +233,6 @@ def grad_accumulate(out, a, b=None, want_sumsq=False):
 
 def clip_coef_from_sq(total_sq: torch.Tensor, max_norm: float):
     """(reference: offload_adam.py:560-561) clamp(max / (norm + 1e-6), max=1)."""
-    norm = torch.sqrt(total_sq.float())
+    norm = _sqrt_rn(total_sq.float())
     coef = torch.clamp(_f32(max_norm, norm.device) / (norm + _f32(1e-6, norm.device)), max=1.0)
     return coef, norm
