@@ -1,3 +1,19 @@
-from .base import QWeightBase
+"""Weight-only quantized tensor subclasses for quantization-aware training."""
 
-__all__ = ["QWeightBase"]
+from .apply import QuantizeReport, quantize_linears, save_quantized_pretrained
+from .base import QWeightBase
+from .int4 import Int4QWeight
+from .int8 import Int8QWeight
+from .nf4 import NF4QWeight
+from .nvfp4 import NVFP4QWeight
+
+__all__ = [
+    "QWeightBase",
+    "Int4QWeight",
+    "Int8QWeight",
+    "NF4QWeight",
+    "NVFP4QWeight",
+    "quantize_linears",
+    "save_quantized_pretrained",
+    "QuantizeReport",
+]
