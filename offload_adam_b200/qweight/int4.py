@@ -46,15 +46,17 @@ def unpack_int4_gptq(packed: Tensor) -> Tensor:
 
 
 @torch.no_grad()
-def quantize_int4_groupwise(tensor: Tensor, group_size: int = 128, eps: float = 1e-12) -> Tuple[Tensor, Tensor]:
-    """PyTorch restatement.  Returns ``(qweight, scales)``, scales in the input dtype."""
+def quantize_int4_groupwise(tensor: Tensor, group_size: int = 128, eps: float = 1e-12,
+                            scale_dtype=None) -> Tuple[Tensor, Tensor]:
+    """PyTorch restatement.  Returns ``(qweight, scales)``; the fp32 scale is rounded once,
+    to ``scale_dtype`` (default: the input dtype)."""
     out_f, in_f = tensor.shape
     assert in_f % group_size == 0, f"in_features={in_f} not divisible by group_size={group_size}"
     assert in_f % 8 == 0, f"in_features={in_f} must be a multiple of 8"
     g = tensor.float().reshape(out_f, in_f // group_size, group_size)
     scale = g.abs().amax(dim=-1) / 8
     q = torch.round(g * (1.0 / scale.clamp(min=eps)).unsqueeze(-1)).clamp(-8, 7).to(torch.int8)
-    return pack_int4_gptq(q.reshape(out_f, in_f)), scale.T.contiguous().to(tensor.dtype)
+    return pack_int4_gptq(q.reshape(out_f, in_f)), scale.T.contiguous().to(scale_dtype or tensor.dtype)
 
 
 def _kernel_ok(in_f: int, group: int, *tensors) -> bool:
@@ -128,7 +130,8 @@ class Int4QWeight(QWeightBase):
                 _kernel_ok(self.shape[1], self.group_size, self.qweight, src):
             _quantize_pack_int4_cuda(src, self.group_size, self.scales.dtype, self.qweight, self.scales)
             return
-        qweight, scales = quantize_int4_groupwise(src.to(self.qweight.device), self.group_size)
+        qweight, scales = quantize_int4_groupwise(src.to(self.qweight.device), self.group_size,
+                                                  scale_dtype=self.scales.dtype)
         self.qweight.copy_(qweight)
         self.scales.copy_(scales)
 

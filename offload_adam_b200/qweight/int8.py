@@ -25,13 +25,14 @@ _BYTE_SHIFTS = (0, 8, 16, 24)
 
 
 @torch.no_grad()
-def quantize_int8_per_channel(tensor: Tensor, eps: float = 1e-12) -> Tuple[Tensor, Tensor]:
-    """PyTorch restatement.  Returns ``(weight int8, scales)``, scales in the input dtype."""
+def quantize_int8_per_channel(tensor: Tensor, eps: float = 1e-12, scale_dtype=None) -> Tuple[Tensor, Tensor]:
+    """PyTorch restatement.  Returns ``(weight int8, scales)``; the fp32 scale is rounded
+    once, to ``scale_dtype`` (default: the input dtype)."""
     assert tensor.ndim == 2
     t = tensor.float()
     scale = t.abs().amax(dim=1) / 127.0
     q = torch.round(t * (1.0 / scale.clamp(min=eps)).unsqueeze(1)).clamp(-128, 127).to(torch.int8)
-    return q, scale.to(tensor.dtype)
+    return q, scale.to(scale_dtype or tensor.dtype)
 
 
 def dequantize_int8_per_channel(weight: Tensor, scales: Tensor) -> Tensor:
@@ -101,7 +102,7 @@ class Int8QWeight(QWeightBase):
         if self.weight.is_cuda and src.is_cuda and src.dtype in _CUDA_DTYPES and self.scales.dtype in _CUDA_DTYPES:
             _quantize_int8_cuda(src, self.scales.dtype, self.weight, self.scales)
             return
-        weight, scales = quantize_int8_per_channel(src.to(self.weight.device))
+        weight, scales = quantize_int8_per_channel(src.to(self.weight.device), scale_dtype=self.scales.dtype)
         self.weight.copy_(weight)
         self.scales.copy_(scales)
 
