@@ -37,17 +37,60 @@ struct Ptrs {
   void* extra;
 };
 
+// Peer-mapped replicas for the fused reduce-scatter / all-gather variant.
+struct Peers {
+  const uint16_t* g[kMaxPeers];
+  uint16_t* p[kMaxPeers];
+  int n_g;
+  int n_p;
+  float g_scale;
+};
+
+// bf16(scale * (a + b + ...)) of two packed bf16 pairs, fp32 accumulation
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
+// 16 gradient values = average of the same 16 values on every rank
+__device__ __forceinline__ V8 pull_reduce_vec(const Peers& pr, int64_t e) {
+  V8 in[kMaxPeers];
+#pragma unroll
+  for (int j = 0; j < kMaxPeers; ++j)
+    if (j < pr.n_g) in[j] = ld32_peer(pr.g[j] + e);
+  V8 out;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    float lo = 0.f, hi = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxPeers; ++j)
+      if (j < pr.n_g) {
+        float2 f = unpack2(in[j].w[w]);
+        lo = __fadd_rn(lo, f.x);
+        hi = __fadd_rn(hi, f.y);
+      }
+    out.w[w] = f32_to_bf16_rne_bits(__fmul_rn(lo, pr.g_scale)) |
+               (f32_to_bf16_rne_bits(__fmul_rn(hi, pr.g_scale)) << 16);
+  }
+  return out;
+}
+__device__ __forceinline__ uint32_t pull_reduce_one(const Peers& pr, int64_t i) {
+  float s = 0.f;
+  for (int j = 0; j < pr.n_g; ++j) s = __fadd_rn(s, bf16_bits_to_f32(pr.g[j][i]));
+  return f32_to_bf16_rne_bits(__fmul_rn(s, pr.g_scale));
+}
+
 template <int MODE>
 struct VecRegs {
   V8 p, g, g2, m, v, e0, e1;
 };
 
-template <int MODE, bool HAS_G2>
-__device__ __forceinline__ void load_vec(VecRegs<MODE>& r, const Ptrs& t, int64_t vec) {
+template <int MODE, bool HAS_G2, bool PEERS>
+__device__ __forceinline__ void load_vec(VecRegs<MODE>& r, const Ptrs& t, const Peers& pr, int64_t vec) {
   const int64_t e = vec * kVec;
   if (MODE != kModeFP32Master) r.p = ld32(t.p + e);  // params stay cacheable (forward re-reads)
-  r.g = ld32_stream(t.g + e);
-  if (HAS_G2) r.g2 = ld32_stream(t.g2 + e);
+  if (PEERS) r.g = pull_reduce_vec(pr, e);
+  else r.g = ld32_stream(t.g + e);
+  if (HAS_G2 && !PEERS) r.g2 = ld32_stream(t.g2 + e);
   r.m = ld32_stream(t.m + e);
   r.v = ld32_stream(t.v + e);
   if (MODE == kModeFP32Master) {
@@ -95,9 +138,9 @@ __device__ __forceinline__ float element_step(uint32_t& p16, uint32_t g16, bool 
   return p;
 }
 
-template <int MODE, bool DECOUPLED, bool HAS_G2>
-__device__ __forceinline__ float compute_store_vec(VecRegs<MODE>& r, const Ptrs& t, int64_t vec,
-                                                   float clip, const AdamScalars& s,
+template <int MODE, bool DECOUPLED, bool HAS_G2, bool PEERS>
+__device__ __forceinline__ float compute_store_vec(VecRegs<MODE>& r, const Ptrs& t, const Peers& pr,
+                                                   int64_t vec, float clip, const AdamScalars& s,
                                                    uint64_t seed, int64_t elem_offset) {
   const int64_t e = vec * kVec;
   Philox4 rnd[2];
@@ -129,7 +172,14 @@ __device__ __forceinline__ float compute_store_vec(VecRegs<MODE>& r, const Ptrs&
     }
     if (MODE == kModeFP31 || MODE == kModeCustom) set_half(r.e0, j, (uint32_t)(uint16_t)err);
   }
-  if (t.p != nullptr) st32(t.p + e, pout);
+  if (PEERS && pr.n_p > 0) {
+    // push the new rows into every replica (all-gather folded into the update)
+#pragma unroll
+    for (int j = 0; j < kMaxPeers; ++j)
+      if (j < pr.n_p) st32(pr.p[j] + e, pout);
+  } else if (t.p != nullptr) {
+    st32(t.p + e, pout);
+  }
   st32_stream(t.m + e, r.m);
   st32_stream(t.v + e, r.v);
   if (MODE == kModeFP32Master) {
@@ -143,10 +193,10 @@ __device__ __forceinline__ float compute_store_vec(VecRegs<MODE>& r, const Ptrs&
 }
 
 // Scalar path: tails and tensors whose pointers are not 32-byte aligned.
-template <int MODE, bool DECOUPLED>
+template <int MODE, bool DECOUPLED, bool PEERS = false>
 __device__ __forceinline__ float scalar_element(const Ptrs& t, int64_t i, bool has_g2, float clip,
                                                 const AdamScalars& s, uint64_t seed,
-                                                int64_t elem_offset) {
+                                                int64_t elem_offset, const Peers* pr = nullptr) {
   uint32_t p16 = (MODE != kModeFP32Master) ? t.p[i] : 0u;
   uint32_t m16 = t.m[i], v16 = t.v[i];
   float master = 0.f;
@@ -159,9 +209,14 @@ __device__ __forceinline__ float scalar_element(const Ptrs& t, int64_t i, bool h
     Philox4 rnd = philox4x32_10((uint64_t)(G >> 3), seed);
     rand16 = philox_word16(rnd, (int)(G & 7));
   }
-  float pf = element_step<MODE, DECOUPLED>(p16, t.g[i], has_g2, has_g2 ? t.g2[i] : 0u, m16, v16,
-                                           master, err, clip, s, rand16);
-  if (t.p != nullptr) t.p[i] = (uint16_t)p16;
+  const uint32_t g16 = PEERS ? pull_reduce_one(*pr, i) : (uint32_t)t.g[i];
+  float pf = element_step<MODE, DECOUPLED>(p16, g16, has_g2 && !PEERS, (has_g2 && !PEERS) ? t.g2[i] : 0u,
+                                           m16, v16, master, err, clip, s, rand16);
+  if (PEERS && pr->n_p > 0) {
+    for (int j = 0; j < pr->n_p; ++j) pr->p[j][i] = (uint16_t)p16;
+  } else if (t.p != nullptr) {
+    t.p[i] = (uint16_t)p16;
+  }
   t.m[i] = (uint16_t)m16;
   t.v[i] = (uint16_t)v16;
   if (MODE == kModeFP32Master) reinterpret_cast<float*>(t.extra)[i] = master;
@@ -169,11 +224,13 @@ __device__ __forceinline__ float scalar_element(const Ptrs& t, int64_t i, bool h
   return fabsf(pf);
 }
 
-template <int MODE, bool DECOUPLED, bool HAS_G2>
+template <int MODE, bool DECOUPLED, bool HAS_G2, bool PEERS>
 __global__ void __launch_bounds__(kThreads)
-adam_step_kernel(Ptrs t, int64_t n, AdamScalars s, const float* __restrict__ clip_ptr,
-                 uint64_t seed, int64_t elem_offset, float* amax_out, int vector_ok) {
+adam_step_kernel(Ptrs t, Peers pr, int64_t n, AdamScalars s, const float* __restrict__ clip_ptr,
+                 uint64_t seed, int64_t elem_offset, float* amax_out, int vector_ok,
+                 const int* abort_flag) {
   __shared__ float red[kThreads / 32];
+  if (abort_flag != nullptr && *reinterpret_cast<const volatile int*>(abort_flag) != 0) return;
   const float clip = clip_ptr ? *clip_ptr : 1.0f;
   float amax = 0.f;
   const int64_t tid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
@@ -184,13 +241,13 @@ adam_step_kernel(Ptrs t, int64_t n, AdamScalars s, const float* __restrict__ cli
     scalar_begin = nvec * kVec;
     for (int64_t vec = tid; vec < nvec; vec += nthreads) {
       VecRegs<MODE> r;
-      load_vec<MODE, HAS_G2>(r, t, vec);
-      amax = fmaxf(amax, compute_store_vec<MODE, DECOUPLED, HAS_G2>(r, t, vec, clip, s, seed,
-                                                                    elem_offset));
+      load_vec<MODE, HAS_G2, PEERS>(r, t, pr, vec);
+      amax = fmaxf(amax, compute_store_vec<MODE, DECOUPLED, HAS_G2, PEERS>(r, t, pr, vec, clip, s,
+                                                                           seed, elem_offset));
     }
   }
   for (int64_t i = scalar_begin + tid; i < n; i += nthreads)
-    amax = fmaxf(amax, scalar_element<MODE, DECOUPLED>(t, i, HAS_G2, clip, s, seed, elem_offset));
+    amax = fmaxf(amax, scalar_element<MODE, DECOUPLED, PEERS>(t, i, HAS_G2, clip, s, seed, elem_offset, &pr));
 
   if (amax_out != nullptr) {
     float bm = block_max<kThreads>(amax, red);
@@ -199,15 +256,18 @@ adam_step_kernel(Ptrs t, int64_t n, AdamScalars s, const float* __restrict__ cli
 }
 
 template <int MODE>
-cudaError_t dispatch(const AdamStepArgs& a, const Ptrs& t, const AdamScalars& s, int grid,
-                     int vector_ok, cudaStream_t st) {
-#define OAB_LAUNCH(DEC, G2)                                                                   \
-  adam_step_kernel<MODE, DEC, G2><<<grid, kThreads, 0, st>>>(t, a.n, s, a.clip_coef, a.seed,  \
-                                                            a.elem_offset, a.amax_out, vector_ok)
-  if (a.decoupled) {
-    if (a.g2) OAB_LAUNCH(true, true); else OAB_LAUNCH(true, false);
+cudaError_t dispatch(const AdamStepArgs& a, const Ptrs& t, const Peers& pr, const AdamScalars& s,
+                     int grid, int vector_ok, cudaStream_t st) {
+#define OAB_LAUNCH(DEC, G2, PE)                                                                \
+  adam_step_kernel<MODE, DEC, G2, PE><<<grid, kThreads, 0, st>>>(                              \
+      t, pr, a.n, s, a.clip_coef, a.seed, a.elem_offset, a.amax_out, vector_ok, a.abort_flag)
+  const bool peers = a.n_g_peers > 0 || a.n_p_peers > 0;
+  if (peers) {
+    if (a.decoupled) OAB_LAUNCH(true, false, true); else OAB_LAUNCH(false, false, true);
+  } else if (a.decoupled) {
+    if (a.g2) OAB_LAUNCH(true, true, false); else OAB_LAUNCH(true, false, false);
   } else {
-    if (a.g2) OAB_LAUNCH(false, true); else OAB_LAUNCH(false, false);
+    if (a.g2) OAB_LAUNCH(false, true, false); else OAB_LAUNCH(false, false, false);
   }
 #undef OAB_LAUNCH
   return cudaGetLastError();
@@ -221,6 +281,18 @@ cudaError_t launch_adam_step(const AdamStepArgs& a, cudaStream_t stream) {
   if (a.mode != kModeSR && a.extra == nullptr) return cudaErrorInvalidValue;
   Ptrs t{(uint16_t*)a.p, (const uint16_t*)a.g, (const uint16_t*)a.g2,
          (uint16_t*)a.m, (uint16_t*)a.v, a.extra};
+  if (a.n_g_peers > kMaxPeers || a.n_p_peers > kMaxPeers) return cudaErrorInvalidValue;
+  if (a.n_g_peers == 0 && a.g == nullptr) return cudaErrorInvalidValue;
+  Peers pr;
+  pr.n_g = a.n_g_peers;
+  pr.n_p = a.n_p_peers;
+  pr.g_scale = a.g_scale;
+  for (int j = 0; j < kMaxPeers; ++j) {
+    pr.g[j] = (const uint16_t*)a.g_peers[j];
+    pr.p[j] = (uint16_t*)a.p_peers[j];
+  }
+  // with a pulled gradient the local `g` is unused; point it somewhere valid
+  if (a.n_g_peers > 0) { t.g = pr.g[0]; t.g2 = nullptr; }
   AdamScalars s;
   s.lr = a.lr;
   s.wd = a.wd;
@@ -229,18 +301,20 @@ cudaError_t launch_adam_step(const AdamStepArgs& a, cudaStream_t stream) {
   s.one_m_b2h = 1.0f - a.beta2_hat;
   s.eps = a.eps;
   auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 31u) == 0; };
-  int vector_ok = al(a.p) && al(a.g) && al(a.g2) && al(a.m) && al(a.v) && al(a.extra) &&
+  int vector_ok = al(a.p) && al(t.g) && al(t.g2) && al(a.m) && al(a.v) && al(a.extra) &&
                   ((a.elem_offset & 7) == 0);
+  for (int j = 0; j < a.n_g_peers; ++j) vector_ok = vector_ok && al(a.g_peers[j]);
+  for (int j = 0; j < a.n_p_peers; ++j) vector_ok = vector_ok && al(a.p_peers[j]);
   const int64_t nvec = (a.n + kVec - 1) / kVec;
   int64_t want = (nvec + kThreads - 1) / kThreads;
   int cap = a.max_ctas > 0 ? a.max_ctas : kNumSMs * 8;
   int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
   count_launch();
   switch (a.mode) {
-    case kModeSR: return dispatch<kModeSR>(a, t, s, grid, vector_ok, stream);
-    case kModeFP32Master: return dispatch<kModeFP32Master>(a, t, s, grid, vector_ok, stream);
-    case kModeFP31: return dispatch<kModeFP31>(a, t, s, grid, vector_ok, stream);
-    case kModeCustom: return dispatch<kModeCustom>(a, t, s, grid, vector_ok, stream);
+    case kModeSR: return dispatch<kModeSR>(a, t, pr, s, grid, vector_ok, stream);
+    case kModeFP32Master: return dispatch<kModeFP32Master>(a, t, pr, s, grid, vector_ok, stream);
+    case kModeFP31: return dispatch<kModeFP31>(a, t, pr, s, grid, vector_ok, stream);
+    case kModeCustom: return dispatch<kModeCustom>(a, t, pr, s, grid, vector_ok, stream);
     default: return cudaErrorInvalidValue;
   }
 }

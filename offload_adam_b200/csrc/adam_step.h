@@ -5,6 +5,8 @@
 
 namespace oab {
 
+constexpr int kMaxPeers = 8;  // ranks of one NVSwitch domain
+
 enum AdamMode : int {
   kModeSR = 0,          // bf16 params, stochastic rounding on write-back
   kModeFP32Master = 1,  // fp32 master copy, bf16 param is RNE(master)
@@ -36,6 +38,21 @@ struct AdamStepArgs {
   float* amax_out = nullptr;         // optional: atomic max of |updated master| (fp32 bits)
   int max_ctas = 0;                  // 0 = size for HBM streaming; small values keep
                                      // most SMs free for concurrent GEMMs
+
+  // ---- ZeRO-1 collectives fused into the same pass (all optional) ----
+  // Gradient pulled from the replicas of every rank (peer-mapped pointers, NVLink):
+  //   g := bf16(g_scale * sum_j g_peers[j][i]), summed in fp32 in index order.
+  // When n_g_peers > 0, `g`/`g2` are ignored.
+  const void* g_peers[kMaxPeers] = {};
+  int n_g_peers = 0;
+  float g_scale = 1.0f;
+  // The updated bf16 parameter is stored to each of these (the replicas of all ranks,
+  // the local one included) instead of `p`; `p` is still the source of the old value.
+  void* p_peers[kMaxPeers] = {};
+  int n_p_peers = 0;
+  // Device-visible status word; when it is non-zero at launch the kernel returns
+  // without touching memory (an earlier bounded wait gave up).
+  const int* abort_flag = nullptr;
 };
 
 // Enqueues one launch on `stream`.  Returns cudaGetLastError().

@@ -9,6 +9,7 @@
 #include "grad_ops.h"
 #include "offload_engine.h"
 #include "pinned_arena.h"
+#include "symm_ops.h"
 
 namespace py = pybind11;
 using at::Tensor;
@@ -45,18 +46,34 @@ void check_contig(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
 }
 
-oab::AdamStepArgs make_args(int64_t mode, const OptT& p, const Tensor& g, const OptT& g2,
+void set_peers(oab::AdamStepArgs& a, const std::vector<int64_t>& g_peers, double g_scale,
+               const std::vector<int64_t>& p_peers, const OptT& status) {
+  TORCH_CHECK(g_peers.size() <= (size_t)oab::kMaxPeers && p_peers.size() <= (size_t)oab::kMaxPeers,
+              "at most ", oab::kMaxPeers, " peers");
+  a.n_g_peers = (int)g_peers.size();
+  a.n_p_peers = (int)p_peers.size();
+  a.g_scale = (float)g_scale;
+  for (size_t j = 0; j < g_peers.size(); ++j) a.g_peers[j] = reinterpret_cast<const void*>(g_peers[j]);
+  for (size_t j = 0; j < p_peers.size(); ++j) a.p_peers[j] = reinterpret_cast<void*>(p_peers[j]);
+  if (status.has_value() && status->defined()) a.abort_flag = reinterpret_cast<const int*>(dev_ptr(*status));
+}
+
+oab::AdamStepArgs make_args(int64_t mode, const OptT& p, const OptT& g_opt, const OptT& g2,
                             const Tensor& m, const Tensor& v, const OptT& extra, double lr,
                             double wd, double b1h, double b2h, double eps, bool decoupled,
                             const OptT& clip, int64_t seed, int64_t elem_offset, const OptT& amax,
                             int64_t max_ctas) {
-  TORCH_CHECK(g.scalar_type() == at::kBFloat16 && m.scalar_type() == at::kBFloat16 &&
-                  v.scalar_type() == at::kBFloat16,
-              "grad/exp_avg/exp_avg_sq must be bfloat16");
-  const int64_t n = g.numel();
-  TORCH_CHECK(m.numel() == n && v.numel() == n, "state size mismatch");
-  check_contig(g, "grad"); check_contig(m, "exp_avg"); check_contig(v, "exp_avg_sq");
+  TORCH_CHECK(m.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16,
+              "exp_avg/exp_avg_sq must be bfloat16");
+  const int64_t n = m.numel();
+  TORCH_CHECK(v.numel() == n, "state size mismatch");
+  check_contig(m, "exp_avg"); check_contig(v, "exp_avg_sq");
   oab::AdamStepArgs a;
+  const bool has_g = g_opt.has_value() && g_opt->defined();
+  if (has_g) {
+    TORCH_CHECK(g_opt->scalar_type() == at::kBFloat16 && g_opt->numel() == n, "grad must be bf16 of the state's size");
+    check_contig(*g_opt, "grad");
+  }
   a.mode = (int)mode;
   a.decoupled = decoupled;
   if (p.has_value() && p->defined()) {
@@ -64,7 +81,7 @@ oab::AdamStepArgs make_args(int64_t mode, const OptT& p, const Tensor& g, const 
     check_contig(*p, "params");
     a.p = dev_ptr(*p);
   }
-  a.g = dev_ptr(g);
+  if (has_g) a.g = dev_ptr(*g_opt);
   if (g2.has_value() && g2->defined()) {
     TORCH_CHECK(g2->scalar_type() == at::kBFloat16 && g2->numel() == n, "grad2 mismatch");
     a.g2 = dev_ptr(*g2);
@@ -97,12 +114,15 @@ oab::AdamStepArgs make_args(int64_t mode, const OptT& p, const Tensor& g, const 
   return a;
 }
 
-void adam_step(int64_t mode, const OptT& p, const Tensor& g, const OptT& g2, const Tensor& m,
+void adam_step(int64_t mode, const OptT& p, const OptT& g, const OptT& g2, const Tensor& m,
                const Tensor& v, const OptT& extra, double lr, double wd, double b1h, double b2h,
                double eps, bool decoupled, const OptT& clip, int64_t seed, int64_t elem_offset,
-               const OptT& amax, int64_t max_ctas, int64_t stream) {
+               const OptT& amax, int64_t max_ctas, int64_t stream, const std::vector<int64_t>& g_peers,
+               double g_scale, const std::vector<int64_t>& p_peers, const OptT& status) {
   auto a = make_args(mode, p, g, g2, m, v, extra, lr, wd, b1h, b2h, eps, decoupled, clip, seed,
                      elem_offset, amax, max_ctas);
+  set_peers(a, g_peers, g_scale, p_peers, status);
+  TORCH_CHECK(a.g != nullptr || a.n_g_peers > 0, "adam_step needs a gradient");
   cu_check(oab::launch_adam_step(a, pick_stream(stream)), "adam_step launch");
 }
 
@@ -238,7 +258,8 @@ struct PyEngine {
   void staged_step(int64_t pid, int64_t mode, const OptT& p, const OptT& g, const OptT& host_grad,
                    const Tensor& m, const Tensor& v, const OptT& extra, double lr, double wd, double b1h,
                    double b2h, double eps, bool decoupled, const OptT& clip, int64_t seed,
-                   int64_t elem_offset, const OptT& amax) {
+                   int64_t elem_offset, const OptT& amax, const std::vector<int64_t>& g_peers,
+                   double g_scale, const std::vector<int64_t>& p_peers, const OptT& status) {
     TORCH_CHECK(!m.is_cuda() && !v.is_cuda(), "staged_step: state tensors must be pinned host tensors");
     oab::StagedStepArgs a;
     a.pid = (int)pid;
@@ -252,7 +273,8 @@ struct PyEngine {
       TORCH_CHECK(!host_grad->is_cuda() && host_grad->numel() == k.n, "host_grad");
       a.host_grad = host_grad->data_ptr();
     }
-    TORCH_CHECK(k.g != nullptr || a.host_grad != nullptr, "staged_step needs a gradient");
+    set_peers(k, g_peers, g_scale, p_peers, status);
+    TORCH_CHECK(k.g != nullptr || a.host_grad != nullptr || k.n_g_peers > 0, "staged_step needs a gradient");
     k.m = m.data_ptr(); k.v = v.data_ptr();
     if (extra.has_value() && extra->defined()) k.extra = extra->data_ptr();
     k.lr = (float)lr; k.wd = (float)wd; k.beta1_hat = (float)b1h; k.beta2_hat = (float)b2h; k.eps = (float)eps;
@@ -287,7 +309,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("m"), py::arg("v"), py::arg("extra"), py::arg("lr"), py::arg("wd"),
         py::arg("beta1_hat"), py::arg("beta2_hat"), py::arg("eps"), py::arg("decoupled"),
         py::arg("clip") = py::none(), py::arg("seed") = 0, py::arg("elem_offset") = 0,
-        py::arg("amax") = py::none(), py::arg("max_ctas") = 0, py::arg("stream") = 0);
+        py::arg("amax") = py::none(), py::arg("max_ctas") = 0, py::arg("stream") = 0,
+        py::arg("g_peers") = std::vector<int64_t>(), py::arg("g_scale") = 1.0,
+        py::arg("p_peers") = std::vector<int64_t>(), py::arg("status") = py::none());
   m.def("grad_accumulate", &grad_accumulate, py::arg("out"), py::arg("a"), py::arg("b"),
         py::arg("sumsq") = py::none(), py::arg("sumsq_accumulate") = false,
         py::arg("scratch") = py::none(), py::arg("max_ctas") = 0, py::arg("stream") = 0);
@@ -321,7 +345,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         oab::EngineOptions o; o.chunk_elems = chunk_elems; o.slots = (int)slots;
         return (int64_t)oab::OffloadEngine::workspace_bytes(o);
       })
-      .def("staged_step", &PyEngine::staged_step)
+      .def("staged_step", &PyEngine::staged_step, py::arg("pid"), py::arg("mode"), py::arg("p"),
+           py::arg("g"), py::arg("host_grad"), py::arg("m"), py::arg("v"), py::arg("extra"),
+           py::arg("lr"), py::arg("wd"), py::arg("beta1_hat"), py::arg("beta2_hat"), py::arg("eps"),
+           py::arg("decoupled"), py::arg("clip"), py::arg("seed"), py::arg("elem_offset"),
+           py::arg("amax"), py::arg("g_peers") = std::vector<int64_t>(), py::arg("g_scale") = 1.0,
+           py::arg("p_peers") = std::vector<int64_t>(), py::arg("status") = py::none())
       .def("staged_grad_to_host", &PyEngine::staged_grad_to_host)
       .def("join", &PyEngine::join)
       .def("synchronize", &PyEngine::synchronize)

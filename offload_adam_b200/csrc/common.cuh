@@ -115,6 +115,17 @@ __device__ __forceinline__ void st32_stream(void* p, const V8& v) {
                "r"(v.w[6]), "r"(v.w[7])
                : "memory");
 }
+// Load from another GPU's memory through a peer mapping (NVLink): a plain,
+// non-multicast 256-bit load that does not allocate in L1.
+__device__ __forceinline__ V8 ld32_peer(const void* p) {
+  V8 v;
+  asm volatile("ld.global.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]),
+                 "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7])
+               : "l"(p)
+               : "memory");
+  return v;
+}
 // j-th 16-bit half of a 16 x bf16 vector
 __device__ __forceinline__ uint32_t half_of(const V8& q, int j) {
   return (q.w[j >> 1] >> (16 * (j & 1))) & 0xffffu;
@@ -157,6 +168,38 @@ __device__ __forceinline__ float block_max(float v, float* smem) {
   }
   __syncthreads();
   return r;
+}
+
+
+// Upper bound on the grid of kernels that reduce through a scratch area: the area
+// holds kMaxPartials floats followed by one 32-bit ticket counter (zero at rest).
+constexpr int kMaxPartials = 148 * 8;
+
+// Two-stage sum whose result does not depend on block scheduling: every block
+// stores one partial, the block drawing the last ticket adds all partials in
+// index order.  Must be reached by all threads of all blocks.
+template <int THREADS>
+__device__ __forceinline__ void grid_sum_to(float acc, float* red, int* is_last_smem, float* scratch,
+                                            float* out, bool accumulate) {
+  float bs = block_sum<THREADS>(acc, red);
+  unsigned int* ticket = reinterpret_cast<unsigned int*>(scratch + kMaxPartials);
+  if (threadIdx.x == 0) {
+    scratch[blockIdx.x] = bs;
+    __threadfence();
+    unsigned int t = atomicAdd(ticket, 1u);
+    *is_last_smem = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (*is_last_smem) {
+    __threadfence();
+    float s = 0.f;
+    for (int i = threadIdx.x; i < (int)gridDim.x; i += THREADS) s += __ldcg(scratch + i);
+    float total = block_sum<THREADS>(s, red);
+    if (threadIdx.x == 0) {
+      *out = accumulate ? (*out + total) : total;
+      *ticket = 0u;  // ready for the next launch on this stream
+    }
+  }
 }
 
 // Number of SMs on a B200; grids are sized as multiples of this.

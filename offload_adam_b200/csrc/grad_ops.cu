@@ -72,28 +72,7 @@ grad_accumulate_kernel(uint16_t* out, const uint16_t* a, const uint16_t* b, int6
   }
   if (!SUMSQ) return;
 
-  // Stage 1: one partial per block.  Stage 2: the block that draws the last
-  // ticket adds the partials in index order, so the result does not depend on
-  // which block finished last.
-  float bs = block_sum<kThreads>(acc, red);
-  unsigned int* ticket = reinterpret_cast<unsigned int*>(scratch + kMaxPartials);
-  if (threadIdx.x == 0) {
-    scratch[blockIdx.x] = bs;
-    __threadfence();
-    unsigned int t = atomicAdd(ticket, 1u);
-    is_last = (t == gridDim.x - 1);
-  }
-  __syncthreads();
-  if (is_last) {
-    __threadfence();
-    float s = 0.f;
-    for (int i = threadIdx.x; i < (int)gridDim.x; i += kThreads) s += __ldcg(scratch + i);
-    float total = block_sum<kThreads>(s, red);
-    if (threadIdx.x == 0) {
-      *sumsq_out = accumulate ? (*sumsq_out + total) : total;
-      *ticket = 0u;  // ready for the next launch on this stream
-    }
-  }
+  grid_sum_to<kThreads>(acc, red, &is_last, scratch, sumsq_out, accumulate != 0);
 }
 
 __global__ void __launch_bounds__(kThreads)

@@ -5,10 +5,9 @@
 
 namespace oab {
 
-// Upper bound on the grid of the reduction kernels; the scratch area handed to
-// them must hold kMaxPartials floats followed by one 32-bit ticket counter.
-constexpr int kMaxPartials = 148 * 8;
-constexpr size_t kSumsqScratchBytes = (kMaxPartials + 4) * sizeof(float);
+// The scratch area handed to the reduction kernels holds 148 * 8 partial sums
+// followed by one 32-bit ticket counter (see common.cuh).
+constexpr size_t kSumsqScratchBytes = (148 * 8 + 4) * sizeof(float);
 
 // out[i] = bf16(a[i] + b[i])   (b == nullptr: out[i] = a[i]; out == nullptr: no store)
 // and, when sumsq_out != nullptr, sumsq_out (+)= sum_i float(out[i])^2, reduced in a

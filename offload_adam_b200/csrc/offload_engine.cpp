@@ -102,11 +102,14 @@ void OffloadEngine::staged_step(const StagedStepArgs& a) {
     c.n = len;
     c.elem_offset = k.elem_offset + off;
     c.p = k.p ? (char*)k.p + 2 * off : nullptr;
-    if (k.g && a.host_grad) { c.g = (const char*)k.g + 2 * off; c.g2 = sg; }
+    if (k.n_g_peers > 0) { c.g = nullptr; c.g2 = nullptr; }
+    else if (k.g && a.host_grad) { c.g = (const char*)k.g + 2 * off; c.g2 = sg; }
     else if (k.g) { c.g = (const char*)k.g + 2 * off; c.g2 = nullptr; }
     else { c.g = sg; c.g2 = nullptr; }
     c.m = sm; c.v = sv; c.extra = xb ? sx : nullptr;
     c.max_ctas = opt_.max_ctas;
+    for (int j = 0; j < k.n_g_peers; ++j) c.g_peers[j] = (const char*)k.g_peers[j] + 2 * off;
+    for (int j = 0; j < k.n_p_peers; ++j) c.p_peers[j] = (char*)k.p_peers[j] + 2 * off;
     check(launch_adam_step(c, compute_), "adam_step");
     check(cudaEventRecord(s.k_done, compute_), "record");
     check(cudaStreamWaitEvent(d2h_, s.k_done, 0), "wait k");

@@ -135,13 +135,16 @@ class TransferEngine:
 
     # ------------------------------------------------------------------- step
     def step(self, pid, param, dev_grad, host_grad, states, hp, step, decoupled, clip=None, seed=0,
-             amax=None, fork=True):
+             amax=None, fork=True, g_peers=None, g_scale=1.0, p_peers=None, status=None):
         """Adam step of one offloaded tensor (or shard).
 
         ``states`` holds the host tensors ``exp_avg``, ``exp_avg_sq`` and, by mode,
         ``master_params`` / ``rounding_error``.  The gradient is ``dev_grad``,
-        ``host_grad`` or bf16(dev_grad + host_grad).  ``param`` may be None when no
-        bf16 write-back is wanted (fp32_master only).
+        ``host_grad`` or bf16(dev_grad + host_grad), or (``g_peers``: peer-mapped
+        addresses of the same rows in every rank's replica) the rank-ordered average
+        pulled over NVLink.  ``p_peers`` makes the kernel store the updated bf16 rows
+        into every replica.  ``param`` may be None when no bf16 write-back is wanted
+        (fp32_master only).
         """
         lr, wd, beta1, beta2, eps = hp
         if self.cuda and fork:
@@ -152,19 +155,20 @@ class TransferEngine:
                 pid, self.mode_id, param, dev_grad, host_grad, states["exp_avg"],
                 states["exp_avg_sq"], extra, float(lr), float(wd), beta_hat(beta1, step),
                 beta_hat(beta2, step), float(eps), bool(decoupled), clip, int(seed), 0, amax,
+                list(g_peers or ()), float(g_scale), list(p_peers or ()), status,
             )
         else:
             st = dict(states)
             if dev_grad is not None:
                 st["grad"], g2 = dev_grad, host_grad
             else:
-                st["grad"], g2 = host_grad, None
+                st["grad"], g2 = host_grad, None  # both None: the gradient comes from g_peers
             adam_step(
                 self.mode_id, param, st, lr, wd, beta1, beta2, eps, step,
                 decoupled_weight_decay=decoupled, seed=seed, clip_coef=clip, grad2=g2, amax=amax,
                 max_ctas=self.max_ctas,
                 stream=self.opt_stream.cuda_stream if self.cuda else 0,
-                use_cuda=self.cuda,
+                use_cuda=self.cuda, g_peers=g_peers, g_scale=g_scale, p_peers=p_peers, status=status,
             )
         self._retain(dev_grad)
 

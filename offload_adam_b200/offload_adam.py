@@ -246,7 +246,11 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         model.register_forward_pre_hook(lambda *_: self._finish_step())
 
     def _state_shape(self, p, key):
-        """Shape of one host state tensor (subclasses shard the non-grad ones)."""
+        """Shape of one host state tensor (subclasses shard the non-grad ones).  With
+        device-resident accumulators no host gradient buffer is needed: the ``grad``
+        entry stays in the state dict as an empty placeholder."""
+        if key == "grad" and self.grad_residency == "device":
+            return (0,)
         return p.shape
 
     def _estimate_pinned_bytes(self, params):
@@ -416,6 +420,10 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
     def _after_param_update(self, p):
         """Hook for subclasses (e.g. all-gather of an updated shard)."""
 
+    def _step_extra(self, p):
+        """Extra keyword arguments of ``TransferEngine.step`` (peer addresses)."""
+        return {}
+
     def _step_offload(self, p, group, clip_coef=None, dev_grad=None):
         """Enqueue the step of one offloaded parameter on the side streams."""
         st = self.state[p]
@@ -424,7 +432,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         if dev_grad is None:
             dev_grad = self._dev_grad.pop(p, None)
         host_grad = st["grad"] if st["host_grad_valid"] else None
-        if dev_grad is None and host_grad is None:
+        extra = self._step_extra(p)
+        if dev_grad is None and host_grad is None and not extra.get("g_peers"):
             st["step"] -= 1
             return
         seed = self._rng.getrandbits(63) if self.mode == "stochastic_rounding" else 0
@@ -436,7 +445,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         else:
             self._engine.step(self._pid[p], self._param_view(p), dev_grad, host_grad, states,
                               self._hp(group), st["step"], self.decoupled_weight_decay,
-                              clip=clip_coef, seed=seed)
+                              clip=clip_coef, seed=seed, **extra)
         st["host_grad_valid"] = False
         self._after_param_update(p)
 
@@ -482,13 +491,15 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                              self.decoupled_weight_decay, clip_coef=clip_coef, seed=seed,
                              zero_grad=True)
             return
+        entry = {e["p"]: e for e in self._inplace_entries}
         for p in params:
             st = self.state[p]
             tensors = {k: st[k] for k in self.offload_state_keys}
+            tensors["grad"] = entry[p]["grad"]  # subclasses may step from a reduced copy
             adam_step(self.mode, p.data, tensors, *self._hp(self._param2group[p]), st["step"],
                       decoupled_weight_decay=self.decoupled_weight_decay, clip_coef=clip_coef,
                       seed=self._rng.getrandbits(63))
-            st["grad"].zero_()
+            tensors["grad"].zero_()
 
     def _finish_step(self):
         """Run what the hooks deferred and make the main stream wait for the side
@@ -582,6 +593,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             dst = self.state[p]
             for k, v in src.items():
                 if isinstance(v, torch.Tensor) and isinstance(dst.get(k), torch.Tensor):
+                    if k == "grad":
+                        continue  # transient accumulator, never part of a resume
                     if v.shape != dst[k].shape or v.dtype != dst[k].dtype:
                         raise ValueError(f"load_offload_state_dict: state '{k}' of param {idx} "
                                          f"has shape/dtype {tuple(v.shape)}/{v.dtype}, expected "

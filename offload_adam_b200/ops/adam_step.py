@@ -52,6 +52,10 @@ def adam_step(
     max_ctas=0,
     stream=0,
     use_cuda=None,
+    g_peers=None,
+    g_scale=1.0,
+    p_peers=None,
+    status=None,
 ):
     mode_id = MODE_IDS[mode] if isinstance(mode, str) else int(mode)
     b1h = beta_hat(beta1, step)
@@ -63,7 +67,7 @@ def adam_step(
     if mode_id == 0 and seed is None:
         seed = random.getrandbits(63)
     seed = int(seed or 0) & ((1 << 63) - 1)
-    g, m, v = states["grad"], states["exp_avg"], states["exp_avg_sq"]
+    g, m, v = states.get("grad"), states["exp_avg"], states["exp_avg_sq"]
     if use_cuda is None:
         use_cuda = _on_gpu(params, g, m, v)
     if use_cuda:
@@ -71,9 +75,11 @@ def adam_step(
         C.adam_step(
             mode_id, params, g, grad2, m, v, extra, float(lr), float(weight_decay), b1h, b2h,
             float(eps), bool(decoupled_weight_decay), clip_coef, seed, int(elem_offset), amax,
-            int(max_ctas), int(stream),
+            int(max_ctas), int(stream), list(g_peers or ()), float(g_scale), list(p_peers or ()),
+            status,
         )
     else:
+        assert not g_peers and not p_peers, "peer-memory arguments need CUDA"
         oracle.adam_step(
             mode_id, params, g, m, v, extra, lr, weight_decay, b1h, b2h, eps,
             decoupled_weight_decay, clip=clip_coef, g2=grad2, seed=seed, elem_offset=elem_offset,

@@ -17,7 +17,7 @@ Two communication back ends implement those three collectives:
                  memory; one kernel per parameter pulls the peers' gradient rows
                  over NVLink, averages them, runs Adam on the shard and pushes
                  the new bf16 rows into every replica (``parallel/symm.py``,
-                 ``csrc/zero1_kernels.cu``).  No NCCL call on that path.
+                 ``csrc/symm_ops.cu``, ``csrc/adam_step.cu``).  No NCCL call on that path.
 ``comm='auto'``  ``symm`` on CUDA with world size > 1 when symmetric memory can
                  be set up, else ``nccl``.
 
@@ -76,7 +76,9 @@ class DistributedOffloadAdam(OffloadAdam):
         return p.data[lo:hi]
 
     def _state_shape(self, p, key):
-        if key != "grad" and self._is_sharded_shape(p):
+        if key == "grad":
+            return super()._state_shape(p, key)
+        if self._is_sharded_shape(p):
             return (p.shape[0] // self._world_size, *p.shape[1:])
         return p.shape
 
@@ -178,9 +180,7 @@ class DistributedOffloadAdam(OffloadAdam):
         grad = self._take_grad(p)
         st = self.state[p]
         grad_ops.grad_accumulate(st["grad"], st["grad"], grad, scratch=self._scratch_main)
-        if self._symm is not None:
-            self._symm.small_grad_ready(p)  # reduced in one bucket at step time
-        else:
+        if self._symm is None:  # the symmetric path averages all small tensors in one bucket later
             self._avg_all_reduce(st["grad"])
             if self._want_norm():
                 grad_ops.grad_accumulate(None, st["grad"], None, sumsq=self._slot(p),
@@ -193,9 +193,12 @@ class DistributedOffloadAdam(OffloadAdam):
     def _grad_hook(self, p):
         if p.grad is None:
             return
+        symm = self._symm is not None and self._symm.handles(p)
         if not self.ready_for_optimizer_step or self._world_size <= 1:
+            if symm:
+                return self._symm.accumulate(p, self._take_grad(p))
             return super()._grad_hook(p)
-        if self._symm is not None:
+        if symm:
             return self._symm.grad_hook_last(p)
         # ---- last micro-batch, torch.distributed collectives
         grad = self._take_grad(p)
@@ -237,8 +240,15 @@ class DistributedOffloadAdam(OffloadAdam):
     def _param_view(self, p):
         return self._shard_slice(p) if p in self._sharded else p.data
 
+    def _step_extra(self, p):
+        if self._symm is not None and self._symm.handles(p):
+            return self._symm.step_extra(p)
+        return {}
+
     def _after_param_update(self, p):
-        if p not in self._sharded or self._symm is not None:
+        if self._symm is not None and self._symm.handles(p):
+            return self._symm.after_param_update(p)
+        if p not in self._sharded:
             return
         with self._side():
             if p in self._quant_params:
@@ -288,8 +298,15 @@ class DistributedOffloadAdam(OffloadAdam):
         return self._clip[0:1]
 
     def _finish_step(self):
-        if self._symm is not None:
-            self._symm.before_finish()
+        if self._symm is None:
+            return super()._finish_step()
+        stepped = self._step_dirty or bool(self._pending_inplace)
+        self._symm.before_finish()
         super()._finish_step()
-        if self._symm is not None:
+        if stepped:
             self._symm.after_finish()
+
+    def synchronize(self):
+        super().synchronize()
+        if self._symm is not None:
+            self._symm.check_status()
