@@ -43,6 +43,10 @@ def _round_up(x, a):
 
 class SymmZero1:
     def __init__(self, opt, model, timeout_ms=30000):
+        import os
+
+        # plain peer mappings only: no NVLS multicast binding for these buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
         self.opt = opt
