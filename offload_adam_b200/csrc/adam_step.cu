@@ -88,7 +88,7 @@ template <int MODE, bool HAS_G2, bool PEERS>
 __device__ __forceinline__ void load_vec(VecRegs<MODE>& r, const Ptrs& t, const Peers& pr, int64_t vec) {
   const int64_t e = vec * kVec;
   if (MODE != kModeFP32Master) r.p = ld32(t.p + e);  // params stay cacheable (forward re-reads)
-  if (PEERS) r.g = pull_reduce_vec(pr, e);
+  if (PEERS && pr.n_g > 0) r.g = pull_reduce_vec(pr, e);  // gradient pulled from all replicas
   else r.g = ld32_stream(t.g + e);
   if (HAS_G2 && !PEERS) r.g2 = ld32_stream(t.g2 + e);
   r.m = ld32_stream(t.m + e);
@@ -209,7 +209,7 @@ __device__ __forceinline__ float scalar_element(const Ptrs& t, int64_t i, bool h
     Philox4 rnd = philox4x32_10((uint64_t)(G >> 3), seed);
     rand16 = philox_word16(rnd, (int)(G & 7));
   }
-  const uint32_t g16 = PEERS ? pull_reduce_one(*pr, i) : (uint32_t)t.g[i];
+  const uint32_t g16 = (PEERS && pr->n_g > 0) ? pull_reduce_one(*pr, i) : (uint32_t)t.g[i];
   float pf = element_step<MODE, DECOUPLED>(p16, g16, has_g2 && !PEERS, (has_g2 && !PEERS) ? t.g2[i] : 0u,
                                            m16, v16, master, err, clip, s, rand16);
   if (PEERS && pr->n_p > 0) {

@@ -79,6 +79,16 @@ def test_fused_pull_adam_push_equals_separate_steps(mode, world):
         assert torch.equal(r, p1)
     for k in st2:
         assert torch.equal(st2[k], st1[k]), k
+    # push only (the clip path): local, already reduced gradient + stores into all replicas
+    p3, st3 = fresh()
+    st3["grad"] = ref_average(grads)
+    replicas = [torch.zeros(n, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    adam_step(mode, p3, st3, *hp, decoupled_weight_decay=True, seed=9, clip_coef=clip,
+              p_peers=[r.data_ptr() for r in replicas])
+    torch.cuda.synchronize()
+    for r in replicas:
+        assert torch.equal(r, p1)
+    assert torch.equal(st3["exp_avg"], st1["exp_avg"])
 
 
 def test_staged_engine_with_peers_matches_direct():
