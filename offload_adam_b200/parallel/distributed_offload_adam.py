@@ -309,4 +309,4 @@ class DistributedOffloadAdam(OffloadAdam):
     def synchronize(self):
         super().synchronize()
         if self._symm is not None:
-            self._symm.check_status()
+            self._symm.check_status(blocking=True)

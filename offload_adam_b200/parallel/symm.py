@@ -145,7 +145,12 @@ class SymmZero1:
         self.small_sq = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.small_reduced_epoch = 0
 
-        self.status = torch.zeros(4, dtype=torch.int32).pin_memory()
+        # Status word of the bounded waits.  It lives in device memory: kernels poll it at
+        # launch, and a word in host memory would make every launch wait for a PCIe read
+        # queued behind the state DMA traffic.  The host sees it through an asynchronous
+        # mirror refreshed at the end of every step.
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        self.status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
         self.local_sq = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.total_sq = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.epoch = 1
@@ -261,10 +266,14 @@ class SymmZero1:
             self.small_sym.zero_()
         self.epoch += 1
         self.check_status()
+        self.status_host.copy_(self.status, non_blocking=True)
 
-    def check_status(self):
-        """Raise if an earlier bounded wait gave up (read without synchronising)."""
-        code = int(self.status[0])
+    def check_status(self, blocking=False):
+        """Raise if an earlier bounded wait gave up.  By default reads the host mirror
+        written at the end of the previous step (no synchronisation)."""
+        if blocking:
+            self.status_host.copy_(self.status)
+        code = int(self.status_host[0])
         if code != 0:
             names = {1: "a peer's gradient", 2: "a peer's parameter rows", 3: "the norm exchange"}
             raise RuntimeError(
