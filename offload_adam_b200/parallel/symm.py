@@ -124,6 +124,7 @@ class SymmZero1:
             p.data = home
             self.grad_view[p] = self.grad_arena[o: o + n * 2].view(torch.bfloat16).view(p.shape)
         self.acc_valid = {p: False for p in self.params}
+        torch.cuda.empty_cache()  # the parameters' old storage goes back to the driver
         ds_elems = {p: p.numel() // self.N for p in self.params}
         self.shard_bytes = {p: ds_elems[p] * 2 for p in self.params}
         # reduced gradient slices (clip path keeps them until step())
