@@ -1,0 +1,127 @@
+"""Pieces shared by the example trainers: model construction, synthetic batches, the
+timed training loop and the JSON summary (reference: examples/e2e_train/train.py:106-233)."""
+
+from __future__ import annotations
+
+import json
+import os
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+from offload_adam_b200.models.llama import (build_llama, llama3_8b, llama3_70b,  # noqa: E402
+                                            tiny_llama)
+
+MODELS = {"llama3-8b": llama3_8b, "llama3-70b": llama3_70b, "tiny": tiny_llama}
+MODES = ["stochastic_rounding", "fp32_master", "fp31_master", "fp32_master_custom_rounding"]
+
+
+def add_common_args(p):
+    p.add_argument("--model-name", default="llama3-8b", choices=list(MODELS))
+    p.add_argument("--layers", type=int, default=None, help="override the number of layers")
+    p.add_argument("--mode", choices=MODES, default="fp32_master")
+    p.add_argument("--tokens-per-sample", type=int, default=2048)
+    p.add_argument("--grad-accum-steps", type=int, default=1)
+    p.add_argument("--steps", type=int, default=10)
+    p.add_argument("--warmup-steps", type=int, default=2)
+    p.add_argument("--lr", type=float, default=1e-4)
+    p.add_argument("--weight-decay", type=float, default=0.01)
+    p.add_argument("--max-grad-norm", type=float, default=None,
+                   help="L2 global-norm clipping; selects the one-shot .step() path")
+    p.add_argument("--numa-node", default="auto", help="'auto', a node id, or 'none'")
+    p.add_argument("--prefetch-policy", choices=["eager", "lazy"], default="eager")
+    p.add_argument("--transfer", choices=["auto", "staged", "zero_copy"], default="auto")
+    p.add_argument("--grad-residency", choices=["auto", "host", "device"], default="auto")
+    p.add_argument("--gradient-checkpointing", action="store_true")
+    p.add_argument("--seed", type=int, default=1234)
+    p.add_argument("--json-output", type=Path)
+
+
+def numa_arg(v):
+    return None if v == "none" else (v if v == "auto" else int(v))
+
+
+def validate(args):
+    if not torch.cuda.is_available():
+        raise RuntimeError("CUDA is required.")
+    for name in ("tokens_per_sample", "grad_accum_steps", "steps"):
+        if getattr(args, name) < 1:
+            raise ValueError(f"--{name.replace('_', '-')} must be >= 1")
+    if not 0 <= args.warmup_steps < args.steps:
+        raise ValueError("--warmup-steps must be in [0, --steps)")
+
+
+def build_model(args, device):
+    cfg = MODELS[args.model_name]()
+    if args.layers is not None:
+        cfg.num_layers = args.layers
+    model = build_llama(cfg, device=device, dtype=torch.bfloat16, seed=args.seed)
+    model.train()
+    if args.gradient_checkpointing:
+        model.gradient_checkpointing_enable()
+    return model
+
+
+def batches(args, vocab, device, batch_size, seed):
+    gen = torch.Generator(device=device).manual_seed(seed)
+    while True:
+        yield torch.randint(0, vocab, (batch_size, args.tokens_per_sample), device=device, generator=gen)
+
+
+def train(args, model, optimizer, batch_size, device, world=1, rank=0, reduce_loss=None, barrier=None):
+    """Synthetic-token training loop; prints one line per step and returns the summary."""
+    vocab = model.config.vocab_size
+    it = batches(args, vocab, device, batch_size, args.seed + rank)
+    tokens_per_step = batch_size * args.tokens_per_sample * args.grad_accum_steps * world
+    times, losses = [], []
+    torch.cuda.reset_peak_memory_stats()
+    for step in range(args.steps):
+        optimizer.zero_grad(set_to_none=True)
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        t0 = time.perf_counter()
+        for micro in range(args.grad_accum_steps):
+            if hasattr(optimizer, "ready_for_optimizer_step"):
+                optimizer.ready_for_optimizer_step = micro == args.grad_accum_steps - 1
+            ids = next(it)
+            loss = model(ids, labels=ids)
+            (loss / args.grad_accum_steps).backward()
+        optimizer.step()
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        dt = time.perf_counter() - t0
+        value = loss.detach().float()
+        if reduce_loss:
+            value = reduce_loss(value)
+        value = value.item()
+        phase = "warmup" if step < args.warmup_steps else "measure"
+        if rank == 0:
+            print(f"step={step + 1}/{args.steps} phase={phase} loss={value:.4f} step_time_s={dt:.4f} "
+                  f"tokens_per_s={tokens_per_step / dt:.1f} "
+                  f"cuda_peak_gb={torch.cuda.max_memory_allocated() / 1024**3:.2f}", flush=True)
+        if step >= args.warmup_steps:
+            times.append(dt)
+            losses.append(value)
+    return {
+        "model_name": args.model_name, "mode": args.mode, "world_size": world,
+        "batch_size": batch_size, "tokens_per_sample": args.tokens_per_sample,
+        "grad_accum_steps": args.grad_accum_steps, "effective_batch_tokens": tokens_per_step,
+        "gradient_checkpointing": args.gradient_checkpointing, "measured_steps": len(times),
+        "warmup_steps": args.warmup_steps, "avg_loss": sum(losses) / len(losses),
+        "avg_step_time_s": sum(times) / len(times),
+        "tokens_per_second": tokens_per_step * len(times) / sum(times),
+        "max_cuda_memory_gb": torch.cuda.max_memory_allocated() / 1024**3,
+    }
+
+
+def emit(args, summary):
+    print(json.dumps(summary, indent=2, sort_keys=True))
+    if args.json_output is not None:
+        args.json_output.parent.mkdir(parents=True, exist_ok=True)
+        args.json_output.write_text(json.dumps(summary, indent=2, sort_keys=True) + "\n", encoding="utf-8")
