@@ -67,7 +67,11 @@ class SymmZero1:
             pass
 
         # ---- which tensors take this path
-        self.params = [p for p in opt._all_params if p in opt._sharded and p not in opt._quant_params]
+        # every offloaded dense tensor: row-sharded ones (pull own rows, push them back) and
+        # replicated ones whose leading dimension does not divide (pull everything, every
+        # rank steps its own replica with identical bits)
+        self.params = [p for p in opt._offload_params if p not in opt._quant_params]
+        self.is_sharded = {p: p in opt._sharded for p in self.params}
         self.index = {p: i for i, p in enumerate(self.params)}
         self.small = list(opt._inplace_entries)
         n_sym = len(self.params)
@@ -125,13 +129,14 @@ class SymmZero1:
             self.grad_view[p] = self.grad_arena[o: o + n * 2].view(torch.bfloat16).view(p.shape)
         self.acc_valid = {p: False for p in self.params}
         torch.cuda.empty_cache()  # the parameters' old storage goes back to the driver
-        ds_elems = {p: p.numel() // self.N for p in self.params}
-        self.shard_bytes = {p: ds_elems[p] * 2 for p in self.params}
+        self.shard_bytes = {p: (p.numel() // self.N if self.is_sharded[p] else p.numel()) * 2
+                            for p in self.params}
         # reduced gradient slices (clip path keeps them until step())
         self.red = {}
         if opt.max_grad_norm is not None:
             for p in self.params:
-                self.red[p] = torch.empty((p.shape[0] // self.N, *p.shape[1:]), dtype=torch.bfloat16, device=self.dev)
+                shape = (p.shape[0] // self.N, *p.shape[1:]) if self.is_sharded[p] else p.shape
+                self.red[p] = torch.empty(shape, dtype=torch.bfloat16, device=self.dev)
 
         # ---- small replicated parameters: accumulate in symmetric memory, step from a
         # local reduced copy
@@ -169,7 +174,9 @@ class SymmZero1:
         return [b + 4 * (region + word) for b in self.ctrl_base]
 
     def _my_rows(self, base, p):
-        return [b + self.off[p] + self.rank * self.shard_bytes[p] for b in base]
+        """Address, in every rank's arena, of the part of ``p`` this rank reduces/updates."""
+        first = self.rank * self.shard_bytes[p] if self.is_sharded[p] else 0
+        return [b + self.off[p] + first for b in base]
 
     def handles(self, p):
         return p in self.index
@@ -210,7 +217,9 @@ class SymmZero1:
 
     def step_extra(self, p):
         """Extra arguments of the Adam pass of a sharded tensor."""
-        kw = {"p_peers": self._my_rows(self.param_base, p), "status": self.status}
+        kw = {"status": self.status}
+        if self.is_sharded[p]:
+            kw["p_peers"] = self._my_rows(self.param_base, p)
         if self.opt._step_in_backward:
             kw.update(g_peers=self._my_rows(self.grad_base, p), g_scale=1.0 / self.N)
         return kw
