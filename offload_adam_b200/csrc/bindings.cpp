@@ -291,7 +291,23 @@ struct PyEngine {
     float* sc = (scratch.has_value() && scratch->defined()) ? reinterpret_cast<float*>(scratch->data_ptr()) : nullptr;
     eng->staged_grad_to_host((int)pid, host_grad.data_ptr(), dev_grad.data_ptr(), dev_grad.numel(), first, sq, sc);
   }
+  int64_t prefetch(int64_t pid, int64_t mode, const OptT& host_grad, const Tensor& m, const Tensor& v,
+                   const OptT& extra, int64_t from_off) {
+    TORCH_CHECK(!m.is_cuda() && !v.is_cuda(), "prefetch: state tensors must be pinned host tensors");
+    oab::StagedStepArgs a;
+    a.pid = (int)pid;
+    a.k.mode = (int)mode;
+    a.k.n = m.numel();
+    a.k.m = m.data_ptr();
+    a.k.v = v.data_ptr();
+    if (extra.has_value() && extra->defined()) a.k.extra = extra->data_ptr();
+    if (host_grad.has_value() && host_grad->defined()) a.host_grad = host_grad->data_ptr();
+    return eng->prefetch(a, from_off);
+  }
   void join(int64_t stream) { eng->join(pick_stream(stream)); }
+  void join_compute(int64_t stream) { eng->join_compute(pick_stream(stream)); }
+  void discard_prefetched() { eng->discard_prefetched(); }
+  int64_t prefetched_chunks() const { return eng->prefetched_chunks(); }
   void synchronize() { py::gil_scoped_release nogil; eng->synchronize(); }
   int64_t bytes_h2d() const { return eng->bytes_h2d(); }
   int64_t bytes_d2h() const { return eng->bytes_d2h(); }
@@ -352,7 +368,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("amax"), py::arg("g_peers") = std::vector<int64_t>(), py::arg("g_scale") = 1.0,
            py::arg("p_peers") = std::vector<int64_t>(), py::arg("status") = py::none())
       .def("staged_grad_to_host", &PyEngine::staged_grad_to_host)
+      .def("prefetch", &PyEngine::prefetch)
       .def("join", &PyEngine::join)
+      .def("join_compute", &PyEngine::join_compute)
+      .def("discard_prefetched", &PyEngine::discard_prefetched)
+      .def("prefetched_chunks", &PyEngine::prefetched_chunks)
       .def("synchronize", &PyEngine::synchronize)
       .def("bytes_h2d", &PyEngine::bytes_h2d)
       .def("bytes_d2h", &PyEngine::bytes_d2h)

@@ -63,39 +63,100 @@ OffloadEngine::~OffloadEngine() {
 }
 
 OffloadEngine::Slot& OffloadEngine::next_slot() {
+  // never hand out a slot that still holds prefetched, unconsumed state
+  if (!loaded_.empty() && loaded_.front() == cursor_) discard_prefetched();
   Slot& s = slots_[cursor_];
   cursor_ = (cursor_ + 1) % (int)slots_.size();
   return s;
+}
+
+void OffloadEngine::load_chunk(Slot& s, const StagedStepArgs& a, int64_t off, int64_t len) {
+  const AdamStepArgs& k = a.k;
+  const int64_t C = opt_.chunk_elems;
+  const size_t xb = elem_extra_bytes(k.mode);
+  char* sg = s.base;
+  char* sm = s.base + 2 * C;
+  char* sv = s.base + 4 * C;
+  char* sx = s.base + 6 * C;
+  if (s.used) check(cudaStreamWaitEvent(h2d_, s.free_ev, 0), "wait slot");
+  if (a.host_grad) {
+    check(cudaMemcpyAsync(sg, (const char*)a.host_grad + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d g");
+    bytes_h2d_ += 2 * len;
+  }
+  check(cudaMemcpyAsync(sm, (const char*)k.m + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d m");
+  check(cudaMemcpyAsync(sv, (const char*)k.v + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d v");
+  bytes_h2d_ += 4 * len;
+  if (xb) {
+    check(cudaMemcpyAsync(sx, (const char*)k.extra + xb * off, xb * len, cudaMemcpyHostToDevice, h2d_), "h2d x");
+    bytes_h2d_ += xb * len;
+  }
+  check(cudaEventRecord(s.h2d_done, h2d_), "record");
+  s.used = true;
+  s.pid = a.pid;
+  s.off = off;
+  s.len = len;
+  s.has_grad = a.host_grad != nullptr;
+}
+
+void OffloadEngine::discard_prefetched() { loaded_.clear(); }
+
+int64_t OffloadEngine::prefetch(const StagedStepArgs& a, int64_t from_off) {
+  const AdamStepArgs& k = a.k;
+  const int64_t C = opt_.chunk_elems;
+  int64_t off = from_off;
+  bool waited = false;
+  while (off < k.n && (int)loaded_.size() < (int)slots_.size() - 1) {
+    if (!waited) {
+      // the host copy must be complete: previous step's write-back of this tensor
+      if (a.pid >= 0 && a.pid < (int)host_ready_.size() && host_ready_set_[a.pid])
+        check(cudaStreamWaitEvent(h2d_, host_ready_[a.pid], 0), "wait host_ready");
+      if (a.host_grad && a.pid >= 0 && a.pid < (int)grad_ready_.size() && grad_ready_set_[a.pid])
+        check(cudaStreamWaitEvent(h2d_, grad_ready_[a.pid], 0), "wait grad_ready");
+      waited = true;
+    }
+    const int64_t len = (k.n - off < C) ? (k.n - off) : C;
+    const int idx = cursor_;
+    Slot& s = next_slot();
+    load_chunk(s, a, off, len);
+    loaded_.push_back(idx);
+    off += len;
+  }
+  return off;
 }
 
 void OffloadEngine::staged_step(const StagedStepArgs& a) {
   const AdamStepArgs& k = a.k;
   const int64_t C = opt_.chunk_elems;
   const size_t xb = elem_extra_bytes(k.mode);
-  if (a.pid >= 0 && a.pid < (int)host_ready_.size() && host_ready_set_[a.pid])
-    check(cudaStreamWaitEvent(h2d_, host_ready_[a.pid], 0), "wait host_ready");
-  if (a.host_grad && a.pid >= 0 && a.pid < (int)grad_ready_.size() && grad_ready_set_[a.pid])
-    check(cudaStreamWaitEvent(h2d_, grad_ready_[a.pid], 0), "wait grad_ready");
+  bool waited = false;
   for (int64_t off = 0; off < k.n; off += C) {
     const int64_t len = (k.n - off < C) ? (k.n - off) : C;
-    Slot& s = next_slot();
+    Slot* sp = nullptr;
+    if (!loaded_.empty()) {
+      Slot& f = slots_[loaded_.front()];
+      if (f.pid == a.pid && f.off == off && f.len == len && f.has_grad == (a.host_grad != nullptr)) {
+        sp = &f;  // already on its way: prefetched
+        loaded_.pop_front();
+      } else {
+        discard_prefetched();  // out-of-order step: give the slots back
+      }
+    }
+    if (sp == nullptr) {
+      if (!waited) {
+        if (a.pid >= 0 && a.pid < (int)host_ready_.size() && host_ready_set_[a.pid])
+          check(cudaStreamWaitEvent(h2d_, host_ready_[a.pid], 0), "wait host_ready");
+        if (a.host_grad && a.pid >= 0 && a.pid < (int)grad_ready_.size() && grad_ready_set_[a.pid])
+          check(cudaStreamWaitEvent(h2d_, grad_ready_[a.pid], 0), "wait grad_ready");
+        waited = true;
+      }
+      sp = &next_slot();
+      load_chunk(*sp, a, off, len);
+    }
+    Slot& s = *sp;
     char* sg = s.base;
     char* sm = s.base + 2 * C;
     char* sv = s.base + 4 * C;
     char* sx = s.base + 6 * C;
-    if (s.used) check(cudaStreamWaitEvent(h2d_, s.free_ev, 0), "wait slot");
-    if (a.host_grad) {
-      check(cudaMemcpyAsync(sg, (const char*)a.host_grad + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d g");
-      bytes_h2d_ += 2 * len;
-    }
-    check(cudaMemcpyAsync(sm, (const char*)k.m + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d m");
-    check(cudaMemcpyAsync(sv, (const char*)k.v + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d v");
-    bytes_h2d_ += 4 * len;
-    if (xb) {
-      check(cudaMemcpyAsync(sx, (const char*)k.extra + xb * off, xb * len, cudaMemcpyHostToDevice, h2d_), "h2d x");
-      bytes_h2d_ += xb * len;
-    }
-    check(cudaEventRecord(s.h2d_done, h2d_), "record");
     check(cudaStreamWaitEvent(compute_, s.h2d_done, 0), "wait h2d");
 
     AdamStepArgs c = k;
@@ -122,7 +183,6 @@ void OffloadEngine::staged_step(const StagedStepArgs& a) {
       bytes_d2h_ += xb * len;
     }
     check(cudaEventRecord(s.free_ev, d2h_), "record");
-    s.used = true;
   }
   if (a.pid >= 0 && a.pid < (int)host_ready_.size()) {
     check(cudaEventRecord(host_ready_[a.pid], d2h_), "record host_ready");
@@ -190,6 +250,11 @@ void OffloadEngine::join(cudaStream_t stream) {
     check(cudaEventRecord(join_ev_[i], src[i]), "record join");
     check(cudaStreamWaitEvent(stream, join_ev_[i], 0), "wait join");
   }
+}
+
+void OffloadEngine::join_compute(cudaStream_t stream) {
+  check(cudaEventRecord(join_ev_[0], compute_), "record join");
+  check(cudaStreamWaitEvent(stream, join_ev_[0], 0), "wait join");
 }
 
 void OffloadEngine::synchronize() {

@@ -19,6 +19,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <deque>
 #include <vector>
 
 #include "adam_step.h"
@@ -49,8 +50,24 @@ class OffloadEngine {
   static size_t workspace_bytes(const EngineOptions& opt);
 
   // Adam step of one tensor through the slot ring.  The caller has already made
-  // the compute stream wait for the gradient producer.
+  // the compute stream wait for the gradient producer.  Chunks that prefetch()
+  // already brought in are consumed in place.
   void staged_step(const StagedStepArgs& a);
+
+  // Early H2D: copies the host state (and host gradient, if given) of the tensor into
+  // free slots, chunk by chunk from `from_off`, before its gradient exists.  Stops when
+  // the ring is full.  Returns the element offset up to which the tensor is now loaded
+  // (== n when complete).  Only the pid, mode, n and host pointers of `a` are used.
+  // Tensors must later be stepped in the order they were prefetched; a step that finds
+  // other chunks at the head of the queue discards them (their H2D is wasted, nothing
+  // else).
+  int64_t prefetch(const StagedStepArgs& a, int64_t from_off);
+  int64_t prefetched_chunks() const { return (int64_t)loaded_.size(); }
+  void discard_prefetched();
+
+  // Makes `stream` wait for the kernels enqueued so far (parameters are updated) but
+  // not for the trailing D2H write-backs of the state.
+  void join_compute(cudaStream_t stream);
 
   // host_grad (+)= dev_grad through the ring, optionally producing sum of squares of
   // the result into *sumsq_out (device pointer).  first == true: plain D2H copy.
@@ -71,8 +88,13 @@ class OffloadEngine {
     char* base = nullptr;
     cudaEvent_t h2d_done = nullptr, k_done = nullptr, free_ev = nullptr;
     bool used = false;
+    // prefetched content, valid while the slot is queued in loaded_
+    int pid = -1;
+    int64_t off = 0, len = 0;
+    bool has_grad = false;
   };
   Slot& next_slot();
+  void load_chunk(Slot& s, const StagedStepArgs& a, int64_t off, int64_t len);
   void check(cudaError_t e, const char* what);
 
   int device_;
@@ -81,6 +103,7 @@ class OffloadEngine {
   std::vector<Slot> slots_;
   size_t slot_bytes_ = 0;
   int cursor_ = 0;
+  std::deque<int> loaded_;  // slots filled by prefetch(), in consumption order
   std::vector<cudaEvent_t> host_ready_;  // per tensor: last D2H of its state finished
   std::vector<char> host_ready_set_;
   std::vector<cudaEvent_t> grad_ready_;  // per tensor: last D2H of its host gradient finished

@@ -32,7 +32,7 @@ from .ops.oracle import MODE_IDS, beta_hat
 
 class TransferEngine:
     def __init__(self, device, mode, n_tensors, transfer="auto", chunk_elems=8 << 20, ring_slots=4,
-                 max_ctas=0, max_inflight_bytes=8 << 30):
+                 max_ctas=0, max_inflight_bytes=8 << 30, staging_bytes=0):
         self.device = torch.device(device)
         self.mode = mode
         self.mode_id = MODE_IDS[mode]
@@ -61,6 +61,9 @@ class TransferEngine:
                 self.d2h_stream = torch.cuda.Stream()
                 self.scratch = grad_ops.sumsq_scratch(self.device)
                 if transfer == "staged":
+                    # the ring doubles as the early-H2D / trailing-D2H staging area
+                    ring_slots = max(int(ring_slots), min(512, int(staging_bytes) // (int(chunk_elems) * 10)))
+                    self.ring_slots = ring_slots
                     nbytes = self.C.OffloadEngine.workspace_bytes(chunk_elems, ring_slots)
                     ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
                     self._native = self.C.OffloadEngine(
@@ -76,15 +79,36 @@ class TransferEngine:
         if self.cuda:
             self.opt_stream.wait_stream(torch.cuda.current_stream(self.device))
 
-    def join_main(self):
-        """The main stream waits for every side-stream operation enqueued so far."""
+    def join_main(self, wait_writeback=True):
+        """The main stream waits for the side-stream work enqueued so far.  With
+        ``wait_writeback=False`` it waits for the kernels only (parameters updated); the
+        D2H write-back of the state may still be in flight and is ordered before any
+        later H2D of the same tensor by the engine."""
         if not self.cuda:
             return
         main = torch.cuda.current_stream(self.device)
         if self._native is not None:
-            self._native.join(main.cuda_stream)
+            if wait_writeback:
+                self._native.join(main.cuda_stream)
+            else:
+                self._native.join_compute(main.cuda_stream)
         else:
             main.wait_stream(self.opt_stream)
+
+    @property
+    def can_prefetch(self):
+        return self._native is not None
+
+    def prefetch(self, pid, states, host_grad=None, from_off=0):
+        """Start the H2D of a tensor's state ahead of its step (staged transfer only).
+        Returns the element offset up to which it is loaded; equal to the tensor's size
+        when everything fit into the ring."""
+        n = states["exp_avg"].numel()
+        if self._native is None:
+            return n
+        extra = states.get("master_params", states.get("rounding_error"))
+        return self._native.prefetch(pid, self.mode_id, host_grad, states["exp_avg"],
+                                     states["exp_avg_sq"], extra, int(from_off))
 
     def synchronize(self):
         if self.cuda:

@@ -92,6 +92,12 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         grad_residency: ``'auto'`` | ``'host'`` | ``'device'``.
         device_grad_budget: bytes of HBM ``'auto'`` may spend on gradient
             accumulators (default: a quarter of the device's memory).
+        staging_bytes: HBM set aside for the slot ring of the staged transfer
+            (default 4 GiB, about what the reference keeps on the GPU as whole state
+            tensors in flight).  State of the first tensors of the next step is brought
+            into it ahead of time and the last write-backs of a step drain from it while
+            the next forward runs, so up to this many bytes per direction leave the
+            exposed part of the step.
         max_ctas: grid cap of the streaming kernels (0: kernel default); small
             values leave the SMs to the concurrent backward GEMMs.
         seed: seeds the stochastic-rounding stream.
@@ -120,7 +126,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                  decoupled_weight_decay=False, inplace_param_threshold=None,
                  prefetch_policy="eager", verbose=0, *, transfer="auto", grad_residency="auto",
                  device_grad_budget=None, chunk_elems=8 << 20, ring_slots=4, max_ctas=0,
-                 max_inflight_bytes=8 << 30, seed=None):
+                 max_inflight_bytes=8 << 30, staging_bytes=4 << 30, seed=None):
         if prefetch_policy not in ("eager", "lazy"):
             raise ValueError(f"prefetch_policy must be 'eager' or 'lazy' (got {prefetch_policy!r})")
         if grad_residency not in ("auto", "host", "device"):
@@ -193,15 +199,6 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                 if p.requires_grad and p not in self._inplace_params:
                     self._prefetch_module.setdefault(p, m)
 
-        self._engine = TransferEngine(
-            self.device, mode, len(params), transfer=transfer, chunk_elems=chunk_elems,
-            ring_slots=ring_slots, max_ctas=max_ctas, max_inflight_bytes=max_inflight_bytes,
-        )
-        self.transfer = self._engine.transfer
-        self.h2d_stream = self._engine.h2d_stream
-        self.d2h_stream = self._engine.d2h_stream
-        self.opt_stream = self._engine.opt_stream
-
         # ---- where gradient accumulators live
         grad_bytes = sum(p.numel() * 2 for p in self._offload_params)
         if grad_residency == "auto":
@@ -212,6 +209,16 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             else:
                 grad_residency = "host"
         self.grad_residency = grad_residency
+        self._engine = TransferEngine(
+            self.device, mode, len(params), transfer=transfer, chunk_elems=chunk_elems,
+            ring_slots=ring_slots, max_ctas=max_ctas, max_inflight_bytes=max_inflight_bytes,
+            staging_bytes=min(int(staging_bytes), self._estimate_pinned_bytes(self._offload_params)),
+        )
+        self.transfer = self._engine.transfer
+        self.h2d_stream = self._engine.h2d_stream
+        self.d2h_stream = self._engine.d2h_stream
+        self.opt_stream = self._engine.opt_stream
+
         self._dev_grad = {}       # param -> accumulated gradient tensor on the device
         self._pending_inplace = []  # small params whose step is due at the next join
         self._normsq = torch.zeros(max(1, len(params)), dtype=torch.float32, device=self.device)
@@ -219,6 +226,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         self._clip = torch.ones(2, dtype=torch.float32, device=self.device)
         self._multi = None
         self._step_dirty = False
+        self._need_prefetch = True
+        self._hook_order_prev, self._hook_order_cur = None, []
         # main-stream reductions get their own scratch: the engine's belongs to its side stream
         self._scratch_main = grad_ops.sumsq_scratch(self.device)
 
@@ -243,7 +252,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                 p.register_post_accumulate_grad_hook(self._grad_hook)
                 st["host_grad_valid"] = False
         # the next forward must see every update even if the caller skipped step()
-        model.register_forward_pre_hook(lambda *_: self._finish_step())
+        model.register_forward_pre_hook(lambda *_: self._on_forward())
 
     def _state_shape(self, p, key):
         """Shape of one host state tensor (subclasses shard the non-grad ones).  With
@@ -429,6 +438,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         st = self.state[p]
         st["step"] += 1
         self._step_dirty = True
+        if self._step_in_backward:
+            self._hook_order_cur.append(p)
         if dev_grad is None:
             dev_grad = self._dev_grad.pop(p, None)
         host_grad = st["grad"] if st["host_grad_valid"] else None
@@ -501,6 +512,34 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                       seed=self._rng.getrandbits(63))
             tensors["grad"].zero_()
 
+    def _on_forward(self):
+        self._finish_step()
+        if self._need_prefetch:
+            self._need_prefetch = False
+            self._prefetch_states()
+
+    def _prefetch_states(self):
+        """First forward of a step: start the H2D of the state of the tensors that will
+        be stepped first, as far as the ring reaches.  Order: parameter order on the
+        clipping path, the hook order of the previous step otherwise."""
+        eng = self._engine
+        if not (self._cuda and eng.can_prefetch and self.grad_residency == "device"):
+            return
+        if self._step_in_backward:
+            order = self._hook_order_prev
+        else:
+            order = [p for g in self.param_groups for p in g["params"] if p not in self._inplace_params]
+        if not order:
+            return
+        for p in order:
+            if p in self._quant_params:
+                break  # takes its own route through a device temporary
+            st = self.state[p]
+            states = {k: st[k] for k in self._non_grad_keys}
+            n = states["exp_avg"].numel()
+            if eng.prefetch(self._pid[p], states) < n:
+                break
+
     def _finish_step(self):
         """Run what the hooks deferred and make the main stream wait for the side
         streams.  Idempotent; called by ``step()`` and before every forward."""
@@ -511,7 +550,9 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             # only a finished step forces the join: gradient write-backs of earlier
             # micro-batches keep overlapping the next forward
             self._step_dirty = False
-            self._engine.join_main()
+            self._engine.join_main(wait_writeback=False)
+            self._need_prefetch = True
+            self._hook_order_prev, self._hook_order_cur = (self._hook_order_cur or self._hook_order_prev), []
 
     # -------------------------------------------------------------- public API
     @torch.no_grad()
@@ -553,6 +594,11 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
     def zero_grad(self, set_to_none=False):
         """No-op: gradients are consumed and cleared by the hooks."""
         return
+
+    def state_dict(self):
+        """Same layout as the reference; waits for write-backs still in flight first."""
+        self.synchronize()
+        return super().state_dict()
 
     def synchronize(self):
         """Block the host until every enqueued transfer and step has finished."""
