@@ -93,8 +93,9 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         device_grad_budget: bytes of HBM ``'auto'`` may spend on gradient
             accumulators (default: a quarter of the device's memory).
         staging_bytes: HBM set aside for the slot ring of the staged transfer
-            (default 4 GiB, about what the reference keeps on the GPU as whole state
-            tensors in flight).  State of the first tensors of the next step is brought
+            (default 8 GiB, capped at this rank's state size; about what the reference
+            keeps on the GPU as whole state tensors in flight: two of the 4.2 GB
+            embedding-sized states of an 8B model).  State of the first tensors of the next step is brought
             into it ahead of time and the last write-backs of a step drain from it while
             the next forward runs, so up to this many bytes per direction leave the
             exposed part of the step.
@@ -126,7 +127,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                  decoupled_weight_decay=False, inplace_param_threshold=None,
                  prefetch_policy="eager", verbose=0, *, transfer="auto", grad_residency="auto",
                  device_grad_budget=None, chunk_elems=8 << 20, ring_slots=4, max_ctas=0,
-                 max_inflight_bytes=8 << 30, staging_bytes=4 << 30, seed=None):
+                 max_inflight_bytes=8 << 30, staging_bytes=8 << 30, seed=None):
         if prefetch_policy not in ("eager", "lazy"):
             raise ValueError(f"prefetch_policy must be 'eager' or 'lazy' (got {prefetch_policy!r})")
         if grad_residency not in ("auto", "host", "device"):
