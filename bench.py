@@ -66,6 +66,7 @@ def parse_args():
     ap.add_argument("--grad-residency", default="auto")
     ap.add_argument("--comm", default="auto", help="distributed path: auto | symm | nccl")
     ap.add_argument("--max-ctas", type=int, default=0)
+    ap.add_argument("--staging-gib", type=float, default=None, help="size of the staging ring (default: optimizer default)")
     ap.add_argument("--grad-ckpt", action="store_true", help="activation checkpointing per layer")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--verbose", type=int, default=0)
@@ -173,6 +174,8 @@ def build_ours(args, preset, device):
                   mode=preset["mode"], decoupled_weight_decay=True, max_grad_norm=preset["max_grad_norm"],
                   verbose=args.verbose, transfer=args.transfer, grad_residency=args.grad_residency,
                   max_ctas=args.max_ctas, seed=1234)
+    if args.staging_gib is not None:
+        common["staging_bytes"] = int(args.staging_gib * 2**30)
     if preset["optimizer"] == "distributed":
         opt = DistributedOffloadAdam(model, comm=args.comm, **common)
     else:
@@ -349,6 +352,7 @@ def main():
                 "transfer": getattr(opt, "transfer", None),
                 "grad_residency": getattr(opt, "grad_residency", "host (reference)"),
                 "comm": getattr(opt, "comm", None),
+                "staging_gib": (getattr(getattr(opt, "_engine", None), "staging_bytes", 0) or 0) / 2**30,
             },
             "exposed_opt_ms": exposed_ms, "peak_gpu_gb": peak_gb, "build_s": t_build,
             "wall_ms_per_step": wall_ms / args.steps, "clocks": clocks,

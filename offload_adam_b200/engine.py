@@ -53,6 +53,7 @@ class TransferEngine:
         self.h2d_stream = self.d2h_stream = self.opt_stream = None
         self._native = None
         self.scratch = None
+        self.staging_bytes = 0
         if self.cuda:
             self.C = _ext.load(required=True)
             with torch.cuda.device(self.device):
@@ -64,6 +65,7 @@ class TransferEngine:
                     # the ring doubles as the early-H2D / trailing-D2H staging area
                     ring_slots = max(int(ring_slots), min(512, int(staging_bytes) // (int(chunk_elems) * 10)))
                     self.ring_slots = ring_slots
+                    self.staging_bytes = ring_slots * int(chunk_elems) * 10
                     nbytes = self.C.OffloadEngine.workspace_bytes(chunk_elems, ring_slots)
                     ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
                     self._native = self.C.OffloadEngine(

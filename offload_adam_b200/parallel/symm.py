@@ -61,10 +61,6 @@ class SymmZero1:
             raise RuntimeError("symmetric-memory path needs grad_residency='device'")
         group = opt._pg
         self.group_name = group.group_name
-        try:
-            symm_mem.enable_symm_mem_for_group(self.group_name)
-        except Exception:
-            pass
 
         # ---- which tensors take this path
         # every offloaded dense tensor: row-sharded ones (pull own rows, push them back) and
