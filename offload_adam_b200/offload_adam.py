@@ -567,6 +567,9 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         if self._step_in_backward:
             self._finish_step()
             return
+        if self.verbose > 1 and self._engine.can_prefetch:
+            print(f"{self._log_prefix()}step: {self._engine._native.prefetched_chunks()} chunk(s) of "
+                  f"{self._engine.ring_slots} slots prefetched", flush=True)
         clip = self._global_clip_coef()
         inplace = []
         for group in self.param_groups:
