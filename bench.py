@@ -243,14 +243,16 @@ def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, de
             loss = loss_fn(ids)
             (loss / ga).backward()
             last = loss.detach()
+        if batches_host is not None:
+            # device -> host read of the step's result; taken before step() so that the
+            # 4-byte copy does not queue behind the state write-backs on the copy engine
+            last = last.float().item()
         if exposed is not None:
             e0 = torch.cuda.Event(enable_timing=True); e0.record()
         opt.step()
         if exposed is not None:
             e1 = torch.cuda.Event(enable_timing=True); e1.record()
             exposed.append((e0, e1))
-        if batches_host is not None:
-            last = last.float().item()  # device -> host read of the step's result
     return last
 
 

@@ -86,9 +86,16 @@ void scalar_exchange(const Tensor& my_value, const std::vector<int64_t>& peer_sl
   ok(oab::launch_scalar_exchange(a, pick(stream)), "scalar_exchange");
 }
 
+void mirror_words(const Tensor& src, const Tensor& dst, int64_t stream) {
+  TORCH_CHECK(src.is_cuda() && src.scalar_type() == at::kInt && dst.scalar_type() == at::kInt &&
+                  dst.numel() >= src.numel() && src.numel() <= 32, "mirror_words: int32, at most 32 words");
+  ok(oab::launch_mirror_words(src.data_ptr<int>(), status_ptr(dst), (int)src.numel(), pick(stream)), "mirror_words");
+}
+
 }  // namespace
 
 void bind_symm(py::module_& m) {
+  m.def("mirror_words", &mirror_words, py::arg("src"), py::arg("dst"), py::arg("stream") = 0);
   m.def("peer_reduce", &peer_reduce, py::arg("out"), py::arg("peers"), py::arg("scale"),
         py::arg("sumsq") = py::none(), py::arg("scratch") = py::none(), py::arg("status") = py::none(),
         py::arg("max_ctas") = 0, py::arg("stream") = 0);

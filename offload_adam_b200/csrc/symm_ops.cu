@@ -129,6 +129,11 @@ __global__ void signal_kernel(SignalPtrs sp, int n, uint32_t value) {
   if ((int)threadIdx.x < n) st_release_sys(sp.p[threadIdx.x], value);
 }
 
+__global__ void mirror_words_kernel(const int* src, int* dst, int n) {
+  // plain stores (to mapped host memory): keeps the DMA engines out of it
+  if ((int)threadIdx.x < n) dst[threadIdx.x] = src[threadIdx.x];
+}
+
 struct ExchangePtrs {
   float* slots[kMaxPeers];
   uint32_t* flags[kMaxPeers];
@@ -207,6 +212,13 @@ cudaError_t launch_signal(uint32_t* const* ptrs_host, int n, uint32_t value, cud
   for (int j = 0; j < kMaxPeers; ++j) sp.p[j] = ptrs_host[j < n ? j : 0];
   count_launch();
   signal_kernel<<<1, 32, 0, stream>>>(sp, n, value);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_mirror_words(const int* src, int* dst, int n, cudaStream_t stream) {
+  if (n <= 0 || n > 32) return cudaErrorInvalidValue;
+  count_launch();
+  mirror_words_kernel<<<1, 32, 0, stream>>>(src, dst, n);
   return cudaGetLastError();
 }
 

@@ -43,6 +43,10 @@ cudaError_t launch_wait_flags(const uint32_t* flags, int n, uint32_t epoch, uint
 // to each of the n addresses (flag words in the peers' memory).
 cudaError_t launch_signal(uint32_t* const* ptrs_host, int n, uint32_t value, cudaStream_t stream);
 
+// dst[i] = src[i] for i < n <= 32, done by a kernel so that a status word can be
+// mirrored into mapped host memory without queueing behind bulk DMA copies.
+cudaError_t launch_mirror_words(const int* src, int* dst, int n, cudaStream_t stream);
+
 // Single-kernel all-reduce(SUM) of one fp32 scalar across ranks: stores *my_value into
 // slot[rank] of every peer, raises flag[rank] there, waits (bounded) for all local
 // flags and writes the rank-ordered sum to *out.

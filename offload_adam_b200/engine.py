@@ -118,17 +118,21 @@ class TransferEngine:
             self.h2d_stream.synchronize()
             self.d2h_stream.synchronize()
 
-    def _retain(self, tensor):
+    def _retain(self, tensor, copied_out=False):
         """Keep a main-stream tensor alive until the side streams are done with it
-        and apply back-pressure on the bytes queued behind PCIe."""
+        and apply back-pressure on the bytes queued behind PCIe.  ``copied_out``: the
+        tensor is also the source of a D2H copy (not only read by kernels)."""
         if not self.cuda or tensor is None:
             return
         tensor.record_stream(self.opt_stream)
-        if self._native is not None:
+        via_d2h = copied_out and self._native is not None
+        if via_d2h:
             tensor.record_stream(self.d2h_stream)
         nbytes = tensor.numel() * tensor.element_size()
         ev = torch.cuda.Event()
-        ev.record(self.d2h_stream if self._native is not None else self.opt_stream)
+        # kernels consume gradients on the optimizer stream; trailing state write-backs on
+        # the D2H stream must not count against the gradient budget
+        ev.record(self.d2h_stream if via_d2h else self.opt_stream)
         self._inflight.append((ev, nbytes))
         self._inflight_bytes += nbytes
         while self._inflight and (self._inflight[0][0].query() or
@@ -157,7 +161,7 @@ class TransferEngine:
                 grad_ops.grad_accumulate(host_grad, dev_grad, None if first else host_grad,
                                          sumsq=sumsq, scratch=self.scratch, max_ctas=self.max_ctas,
                                          stream=s, use_cuda=True)
-        self._retain(dev_grad)
+        self._retain(dev_grad, copied_out=True)
 
     # ------------------------------------------------------------------- step
     def step(self, pid, param, dev_grad, host_grad, states, hp, step, decoupled, clip=None, seed=0,

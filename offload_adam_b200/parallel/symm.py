@@ -272,7 +272,8 @@ class SymmZero1:
             self.small_sym.zero_()
         self.epoch += 1
         self.check_status()
-        self.status_host.copy_(self.status, non_blocking=True)
+        # a kernel, not a DMA copy: a copy would queue behind the trailing state write-backs
+        self.C.mirror_words(self.status, self.status_host)
 
     def check_status(self, blocking=False):
         """Raise if an earlier bounded wait gave up.  By default reads the host mirror
