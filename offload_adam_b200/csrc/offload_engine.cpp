@@ -100,12 +100,15 @@ void OffloadEngine::load_chunk(Slot& s, const StagedStepArgs& a, int64_t off, in
 
 void OffloadEngine::discard_prefetched() { loaded_.clear(); }
 
-int64_t OffloadEngine::prefetch(const StagedStepArgs& a, int64_t from_off) {
+int64_t OffloadEngine::prefetch(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks) {
   const AdamStepArgs& k = a.k;
   const int64_t C = opt_.chunk_elems;
   int64_t off = from_off;
   bool waited = false;
-  while (off < k.n && (int)loaded_.size() < (int)slots_.size() - 1) {
+  int64_t issued = 0;
+  while (off < k.n && (int)loaded_.size() < (int)slots_.size() - 1 &&
+         (max_chunks <= 0 || issued < max_chunks)) {
+    ++issued;
     if (!waited) {
       // the host copy must be complete: previous step's write-back of this tensor
       if (a.pid >= 0 && a.pid < (int)host_ready_.size() && host_ready_set_[a.pid])

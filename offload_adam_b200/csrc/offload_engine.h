@@ -61,7 +61,9 @@ class OffloadEngine {
   // Tensors must later be stepped in the order they were prefetched; a step that finds
   // other chunks at the head of the queue discards them (their H2D is wasted, nothing
   // else).
-  int64_t prefetch(const StagedStepArgs& a, int64_t from_off);
+  // At most `max_chunks` chunks are issued per call (<= 0: no limit), so that callers can
+  // pace the bulk copies and leave gaps in the copy-engine queue for other traffic.
+  int64_t prefetch(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks);
   int64_t prefetched_chunks() const { return (int64_t)loaded_.size(); }
   void discard_prefetched();
 

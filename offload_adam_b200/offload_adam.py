@@ -227,8 +227,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         self._clip = torch.ones(2, dtype=torch.float32, device=self.device)
         self._multi = None
         self._step_dirty = False
-        self._need_prefetch = True
         self._hook_order_prev, self._hook_order_cur = None, []
+        self._pf_order, self._pf_idx, self._pf_off = None, 0, 0
         # main-stream reductions get their own scratch: the engine's belongs to its side stream
         self._scratch_main = grad_ops.sumsq_scratch(self.device)
 
@@ -387,6 +387,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
     def _grad_hook(self, p):
         if p.grad is None:
             return
+        self._pace_prefetch(1)
         grad = self._take_grad(p)
         st = self.state[p]
         last = self.ready_for_optimizer_step
@@ -515,14 +516,13 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
 
     def _on_forward(self):
         self._finish_step()
-        if self._need_prefetch:
-            self._need_prefetch = False
-            self._prefetch_states()
+        self._pace_prefetch(4)
 
-    def _prefetch_states(self):
-        """First forward of a step: start the H2D of the state of the tensors that will
-        be stepped first, as far as the ring reaches.  Order: parameter order on the
-        clipping path, the hook order of the previous step otherwise."""
+    def _start_prefetch(self):
+        """Begin a new round of early H2D for the step that has just started.  Order:
+        parameter order on the clipping path, the hook order of the previous step
+        otherwise."""
+        self._pf_order, self._pf_idx, self._pf_off = None, 0, 0
         eng = self._engine
         if not (self._cuda and eng.can_prefetch and self.grad_residency == "device"):
             return
@@ -530,16 +530,38 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             order = self._hook_order_prev
         else:
             order = [p for g in self.param_groups for p in g["params"] if p not in self._inplace_params]
-        if not order:
+        self._pf_order = order or None
+
+    def _pace_prefetch(self, max_chunks):
+        """Issue a few more chunks of early H2D.  Called from the forward pre-hook and
+        from every gradient hook: the bulk copies are spread over the step instead of
+        being queued at once, so copies of the caller (input batches) never wait behind
+        more than a few chunks in the copy engine."""
+        order = self._pf_order
+        if order is None:
             return
-        for p in order:
+        eng = self._engine
+        while max_chunks > 0:
+            if self._pf_idx >= len(order):
+                self._pf_order = None
+                return
+            p = order[self._pf_idx]
             if p in self._quant_params:
-                break  # takes its own route through a device temporary
+                self._pf_order = None  # takes its own route through a device temporary
+                return
             st = self.state[p]
             states = {k: st[k] for k in self._non_grad_keys}
             n = states["exp_avg"].numel()
-            if eng.prefetch(self._pid[p], states) < n:
-                break
+            off, issued = eng.prefetch(self._pid[p], states, None, self._pf_off, max_chunks)
+            max_chunks -= issued
+            if off >= n:
+                self._pf_idx += 1
+                self._pf_off = 0
+            else:
+                self._pf_off = off
+                if issued == 0 or max_chunks > 0:
+                    self._pf_order = None  # ring is full
+                    return
 
     def _finish_step(self):
         """Run what the hooks deferred and make the main stream wait for the side
@@ -552,8 +574,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             # micro-batches keep overlapping the next forward
             self._step_dirty = False
             self._engine.join_main(wait_writeback=False)
-            self._need_prefetch = True
             self._hook_order_prev, self._hook_order_cur = (self._hook_order_cur or self._hook_order_prev), []
+            self._start_prefetch()
 
     # -------------------------------------------------------------- public API
     @torch.no_grad()

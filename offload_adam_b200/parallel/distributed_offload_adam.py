@@ -196,8 +196,10 @@ class DistributedOffloadAdam(OffloadAdam):
         symm = self._symm is not None and self._symm.handles(p)
         if not self.ready_for_optimizer_step or self._world_size <= 1:
             if symm:
+                self._pace_prefetch(1)
                 return self._symm.accumulate(p, self._take_grad(p))
             return super()._grad_hook(p)
+        self._pace_prefetch(1)
         if symm:
             return self._symm.grad_hook_last(p)
         # ---- last micro-batch, torch.distributed collectives
