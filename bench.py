@@ -226,7 +226,7 @@ def build_reference(args, preset, device):
 
 # ------------------------------------------------------------------------ training
 def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, device=None,
-              exposed=None):
+              exposed=None, read_loss=lambda t: t.float().item()):
     """One entry of ``batches_*`` per micro-batch (cycled).  With ``batches_host`` the
     ids are copied from pinned memory every micro-batch and the loss is read back every
     step (end-to-end mode)."""
@@ -243,16 +243,14 @@ def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, de
             loss = loss_fn(ids)
             (loss / ga).backward()
             last = loss.detach()
-        if batches_host is not None:
-            # device -> host read of the step's result; taken before step() so that the
-            # 4-byte copy does not queue behind the state write-backs on the copy engine
-            last = last.float().item()
         if exposed is not None:
             e0 = torch.cuda.Event(enable_timing=True); e0.record()
         opt.step()
         if exposed is not None:
             e1 = torch.cuda.Event(enable_timing=True); e1.record()
             exposed.append((e0, e1))
+        if batches_host is not None:
+            last = read_loss(last)  # device -> host read of the step's result (4 bytes)
     return last
 
 
@@ -323,8 +321,15 @@ def main():
 
     e2e = None
     if not args.skip_e2e:
+        if args.impl == "ours":
+            # the package's scalar read: a kernel store into mapped host memory, which
+            # does not queue behind the optimizer's bulk write-backs in the copy engine
+            from offload_adam_b200.utils.scalar import read_scalar as read_loss
+        else:
+            read_loss = lambda t: t.float().item()  # noqa: E731
         ms2, wall2, last_loss = timed(lambda: run_steps(args.steps, ga, opt, loss_fn,
-                                                        batches_host=host_batches, device=device), device)
+                                                        batches_host=host_batches, device=device,
+                                                        read_loss=read_loss), device)
         ms2 = max_over_ranks(max(ms2, 0.0), device)
         wall2 = max_over_ranks(wall2, device)
         # the loss read-back makes the host wait for the device, so wall time and

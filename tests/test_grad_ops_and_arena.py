@@ -133,3 +133,11 @@ def test_arena_is_pinned_and_device_mapped():
     assert torch.equal(g, (src.float() * 2).to(torch.bfloat16).cpu())
     t = pinned_alloc.zeros_pinned((5, 7), torch.int16)
     assert t.is_pinned() and t.shape == (5, 7) and int(t.abs().sum()) == 0
+
+
+@pytest.mark.gpu
+def test_read_scalar_bypasses_copy_engine():
+    from offload_adam_b200.utils.scalar import read_scalar
+    assert read_scalar(torch.tensor(3.25, device="cuda")) == 3.25
+    assert read_scalar(torch.tensor([-7.5], device="cuda", dtype=torch.bfloat16)) == -7.5
+    assert read_scalar(torch.tensor(1.5)) == 1.5
