@@ -292,7 +292,7 @@ struct PyEngine {
     eng->staged_grad_to_host((int)pid, host_grad.data_ptr(), dev_grad.data_ptr(), dev_grad.numel(), first, sq, sc);
   }
   int64_t prefetch(int64_t pid, int64_t mode, const OptT& host_grad, const Tensor& m, const Tensor& v,
-                   const OptT& extra, int64_t from_off, int64_t max_chunks) {
+                   const OptT& extra, int64_t from_off, int64_t max_chunks, int64_t max_inflight) {
     TORCH_CHECK(!m.is_cuda() && !v.is_cuda(), "prefetch: state tensors must be pinned host tensors");
     oab::StagedStepArgs a;
     a.pid = (int)pid;
@@ -302,7 +302,7 @@ struct PyEngine {
     a.k.v = v.data_ptr();
     if (extra.has_value() && extra->defined()) a.k.extra = extra->data_ptr();
     if (host_grad.has_value() && host_grad->defined()) a.host_grad = host_grad->data_ptr();
-    return eng->prefetch(a, from_off, max_chunks);
+    return eng->prefetch(a, from_off, max_chunks, (int)max_inflight);
   }
   void join(int64_t stream) { eng->join(pick_stream(stream)); }
   void join_compute(int64_t stream) { eng->join_compute(pick_stream(stream)); }

@@ -98,9 +98,13 @@ void OffloadEngine::load_chunk(Slot& s, const StagedStepArgs& a, int64_t off, in
   s.has_grad = a.host_grad != nullptr;
 }
 
-void OffloadEngine::discard_prefetched() { loaded_.clear(); }
+void OffloadEngine::discard_prefetched() {
+  loaded_.clear();
+  inflight_.clear();
+}
 
-int64_t OffloadEngine::prefetch(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks) {
+int64_t OffloadEngine::prefetch(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks,
+                                int max_inflight) {
   const AdamStepArgs& k = a.k;
   const int64_t C = opt_.chunk_elems;
   int64_t off = from_off;
@@ -108,6 +112,12 @@ int64_t OffloadEngine::prefetch(const StagedStepArgs& a, int64_t from_off, int64
   int64_t issued = 0;
   while (off < k.n && (int)loaded_.size() < (int)slots_.size() - 1 &&
          (max_chunks <= 0 || issued < max_chunks)) {
+    if (max_inflight > 0) {
+      while (!inflight_.empty() && cudaEventQuery(slots_[inflight_.front()].h2d_done) == cudaSuccess)
+        inflight_.pop_front();
+      (void)cudaGetLastError();  // cudaErrorNotReady is not an error
+      if ((int)inflight_.size() >= max_inflight) break;
+    }
     ++issued;
     if (!waited) {
       // the host copy must be complete: previous step's write-back of this tensor
@@ -122,6 +132,7 @@ int64_t OffloadEngine::prefetch(const StagedStepArgs& a, int64_t from_off, int64
     Slot& s = next_slot();
     load_chunk(s, a, off, len);
     loaded_.push_back(idx);
+    if (max_inflight > 0) inflight_.push_back(idx);
     off += len;
   }
   return off;

@@ -63,7 +63,10 @@ class OffloadEngine {
   // else).
   // At most `max_chunks` chunks are issued per call (<= 0: no limit), so that callers can
   // pace the bulk copies and leave gaps in the copy-engine queue for other traffic.
-  int64_t prefetch(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks);
+  // With max_inflight > 0 a chunk is issued only while fewer than that many earlier
+  // prefetch copies are still running (checked with cudaEventQuery, never blocking), which
+  // bounds how long somebody else's H2D copy can wait behind ours.
+  int64_t prefetch(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks, int max_inflight = 0);
   int64_t prefetched_chunks() const { return (int64_t)loaded_.size(); }
   void discard_prefetched();
 
@@ -106,6 +109,7 @@ class OffloadEngine {
   size_t slot_bytes_ = 0;
   int cursor_ = 0;
   std::deque<int> loaded_;  // slots filled by prefetch(), in consumption order
+  std::deque<int> inflight_;  // prefetch copies possibly still running (slot indices)
   std::vector<cudaEvent_t> host_ready_;  // per tensor: last D2H of its state finished
   std::vector<char> host_ready_set_;
   std::vector<cudaEvent_t> grad_ready_;  // per tensor: last D2H of its host gradient finished

@@ -101,18 +101,20 @@ class TransferEngine:
     def can_prefetch(self):
         return self._native is not None
 
-    def prefetch(self, pid, states, host_grad=None, from_off=0, max_chunks=0):
+    def prefetch(self, pid, states, host_grad=None, from_off=0, max_chunks=0, max_inflight=0):
         """Start the H2D of a tensor's state ahead of its step (staged transfer only),
         at most ``max_chunks`` chunks of it (0: as many as fit).  Returns
         ``(offset, issued)``: the element offset up to which the tensor is loaded and the
-        number of chunks this call issued."""
+        number of chunks this call issued.  ``max_inflight`` > 0 issues nothing while that
+        many earlier prefetch copies are still running."""
         n = states["exp_avg"].numel()
         if self._native is None:
             return n, 0
         extra = states.get("master_params", states.get("rounding_error"))
         before = self._native.prefetched_chunks()
         off = self._native.prefetch(pid, self.mode_id, host_grad, states["exp_avg"],
-                                    states["exp_avg_sq"], extra, int(from_off), int(max_chunks))
+                                    states["exp_avg_sq"], extra, int(from_off), int(max_chunks),
+                                    int(max_inflight))
         return off, self._native.prefetched_chunks() - before
 
     def synchronize(self):

@@ -516,7 +516,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
 
     def _on_forward(self):
         self._finish_step()
-        self._pace_prefetch(4)
+        self._pace_prefetch(1)
 
     def _start_prefetch(self):
         """Begin a new round of early H2D for the step that has just started.  Order:
@@ -552,16 +552,17 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             st = self.state[p]
             states = {k: st[k] for k in self._non_grad_keys}
             n = states["exp_avg"].numel()
-            off, issued = eng.prefetch(self._pid[p], states, None, self._pf_off, max_chunks)
+            before = eng._native.prefetched_chunks()
+            off, issued = eng.prefetch(self._pid[p], states, None, self._pf_off, max_chunks, max_inflight=1)
             max_chunks -= issued
             if off >= n:
                 self._pf_idx += 1
                 self._pf_off = 0
             else:
                 self._pf_off = off
-                if issued == 0 or max_chunks > 0:
+                if before + issued >= eng.ring_slots - 1:
                     self._pf_order = None  # ring is full
-                    return
+                return  # budget used up, or an earlier copy is still in flight: try later
 
     def _finish_step(self):
         """Run what the hooks deferred and make the main stream wait for the side
