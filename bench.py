@@ -227,16 +227,30 @@ def build_reference(args, preset, device):
 # ------------------------------------------------------------------------ training
 def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, device=None,
               exposed=None, read_loss=lambda t: t.float().item()):
-    """One entry of ``batches_*`` per micro-batch (cycled).  With ``batches_host`` the
-    ids are copied from pinned memory every micro-batch and the loss is read back every
-    step (end-to-end mode)."""
+    """One entry of ``batches_*`` per micro-batch (cycled).  With ``batches_host``
+    (end-to-end mode) the token ids of a step are copied from pinned host memory at the
+    start of that step, on a side stream as a data loader would, and the step's loss is
+    read back to the host after ``step()``."""
     last = None
     k = 0
+    copy_stream = torch.cuda.Stream(device) if batches_host is not None else None
     for _ in range(n_steps):
+        staged = None
+        if batches_host is not None:
+            staged = []
+            copy_stream.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(copy_stream):
+                for micro in range(ga):
+                    t = batches_host[(k + micro) % len(batches_host)].to(device, non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(copy_stream)
+                    staged.append((t, ev))
         for micro in range(ga):
             opt.ready_for_optimizer_step = micro == ga - 1
-            if batches_host is not None:
-                ids = batches_host[k % len(batches_host)].to(device, non_blocking=True)
+            if staged is not None:
+                ids, ev = staged[micro]
+                torch.cuda.current_stream(device).wait_event(ev)
+                ids.record_stream(torch.cuda.current_stream(device))
             else:
                 ids = batches_dev[k % len(batches_dev)]
             k += 1

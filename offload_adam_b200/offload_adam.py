@@ -254,6 +254,11 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                 st["host_grad_valid"] = False
         # the next forward must see every update even if the caller skipped step()
         model.register_forward_pre_hook(lambda *_: self._on_forward())
+        # pacing points for the early H2D during forward (plain forward hooks add no
+        # autograd nodes)
+        for m in modules:
+            if any(p.requires_grad and p not in self._inplace_params for p in m.parameters()):
+                m.register_forward_pre_hook(lambda *_: self._pace_prefetch(1))
 
     def _state_shape(self, p, key):
         """Shape of one host state tensor (subclasses shard the non-grad ones).  With
