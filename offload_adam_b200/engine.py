@@ -63,7 +63,7 @@ class TransferEngine:
                 self.scratch = grad_ops.sumsq_scratch(self.device)
                 if transfer == "staged":
                     # the ring doubles as the early-H2D / trailing-D2H staging area
-                    ring_slots = max(int(ring_slots), min(512, int(staging_bytes) // (int(chunk_elems) * 10)))
+                    ring_slots = max(int(ring_slots), min(1024, int(staging_bytes) // (int(chunk_elems) * 10)))
                     self.ring_slots = ring_slots
                     self.staging_bytes = ring_slots * int(chunk_elems) * 10
                     nbytes = self.C.OffloadEngine.workspace_bytes(chunk_elems, ring_slots)

@@ -92,6 +92,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         grad_residency: ``'auto'`` | ``'host'`` | ``'device'``.
         device_grad_budget: bytes of HBM ``'auto'`` may spend on gradient
             accumulators (default: a quarter of the device's memory).
+        chunk_elems: elements per staged chunk (default 8 Mi divided by the world size,
+            at least 1 Mi).
         staging_bytes: HBM set aside for the slot ring of the staged transfer
             (default 8 GiB, capped at this rank's state size; about what the reference
             keeps on the GPU as whole state tensors in flight: two of the 4.2 GB
@@ -126,7 +128,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                  mode="stochastic_rounding", max_grad_norm=None, numa_node="auto",
                  decoupled_weight_decay=False, inplace_param_threshold=None,
                  prefetch_policy="eager", verbose=0, *, transfer="auto", grad_residency="auto",
-                 device_grad_budget=None, chunk_elems=8 << 20, ring_slots=4, max_ctas=0,
+                 device_grad_budget=None, chunk_elems=None, ring_slots=4, max_ctas=0,
                  max_inflight_bytes=8 << 30, staging_bytes=8 << 30, seed=None):
         if prefetch_policy not in ("eager", "lazy"):
             raise ValueError(f"prefetch_policy must be 'eager' or 'lazy' (got {prefetch_policy!r})")
@@ -210,6 +212,10 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             else:
                 grad_residency = "host"
         self.grad_residency = grad_residency
+        if chunk_elems is None:
+            # a slot holds one chunk of one tensor: keep chunks near the size of a typical
+            # (sharded) tensor so that small tensors do not waste ring space
+            chunk_elems = max(1 << 20, (8 << 20) // max(1, getattr(self, "_world_size", 1)))
         self._engine = TransferEngine(
             self.device, mode, len(params), transfer=transfer, chunk_elems=chunk_elems,
             ring_slots=ring_slots, max_ctas=max_ctas, max_inflight_bytes=max_inflight_bytes,
