@@ -243,11 +243,10 @@ struct PyEngine {
   std::unique_ptr<oab::OffloadEngine> eng;
   Tensor workspace;  // keeps the slot ring alive
   PyEngine(int64_t device, int64_t compute, int64_t h2d, int64_t d2h, Tensor ws, int64_t chunk_elems,
-           int64_t slots, int64_t max_ctas, int64_t n_tensors)
+           int64_t max_ctas, int64_t n_tensors)
       : workspace(std::move(ws)) {
     oab::EngineOptions o;
     o.chunk_elems = chunk_elems;
-    o.slots = (int)slots;
     o.max_ctas = (int)max_ctas;
     TORCH_CHECK(workspace.is_cuda(), "engine workspace must be a CUDA tensor");
     eng = std::make_unique<oab::OffloadEngine>(
@@ -291,8 +290,9 @@ struct PyEngine {
     float* sc = (scratch.has_value() && scratch->defined()) ? reinterpret_cast<float*>(scratch->data_ptr()) : nullptr;
     eng->staged_grad_to_host((int)pid, host_grad.data_ptr(), dev_grad.data_ptr(), dev_grad.numel(), first, sq, sc);
   }
-  int64_t prefetch(int64_t pid, int64_t mode, const OptT& host_grad, const Tensor& m, const Tensor& v,
-                   const OptT& extra, int64_t from_off, int64_t max_chunks, int64_t max_inflight) {
+  std::pair<int64_t, bool> prefetch(int64_t pid, int64_t mode, const OptT& host_grad, const Tensor& m,
+                                    const Tensor& v, const OptT& extra, int64_t from_off,
+                                    int64_t max_chunks, int64_t max_inflight) {
     TORCH_CHECK(!m.is_cuda() && !v.is_cuda(), "prefetch: state tensors must be pinned host tensors");
     oab::StagedStepArgs a;
     a.pid = (int)pid;
@@ -302,12 +302,16 @@ struct PyEngine {
     a.k.v = v.data_ptr();
     if (extra.has_value() && extra->defined()) a.k.extra = extra->data_ptr();
     if (host_grad.has_value() && host_grad->defined()) a.host_grad = host_grad->data_ptr();
-    return eng->prefetch(a, from_off, max_chunks, (int)max_inflight);
+    bool full = false;
+    int64_t off = eng->prefetch(a, from_off, max_chunks, (int)max_inflight, &full);
+    return {off, full};
   }
   void join(int64_t stream) { eng->join(pick_stream(stream)); }
   void join_compute(int64_t stream) { eng->join_compute(pick_stream(stream)); }
   void discard_prefetched() { eng->discard_prefetched(); }
   int64_t prefetched_chunks() const { return eng->prefetched_chunks(); }
+  int64_t prefetched_bytes() const { return eng->prefetched_bytes(); }
+  int64_t ring_bytes() const { return (int64_t)eng->ring_bytes(); }
   void synchronize() { py::gil_scoped_release nogil; eng->synchronize(); }
   int64_t bytes_h2d() const { return eng->bytes_h2d(); }
   int64_t bytes_d2h() const { return eng->bytes_d2h(); }
@@ -356,10 +360,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("stats", &PyArena::stats);
 
   py::class_<PyEngine>(m, "OffloadEngine")
-      .def(py::init<int64_t, int64_t, int64_t, int64_t, Tensor, int64_t, int64_t, int64_t, int64_t>())
-      .def_static("workspace_bytes", [](int64_t chunk_elems, int64_t slots) {
-        oab::EngineOptions o; o.chunk_elems = chunk_elems; o.slots = (int)slots;
-        return (int64_t)oab::OffloadEngine::workspace_bytes(o);
+      .def(py::init<int64_t, int64_t, int64_t, int64_t, Tensor, int64_t, int64_t, int64_t>())
+      .def_static("min_ring_bytes", [](int64_t chunk_elems) {
+        return (int64_t)oab::OffloadEngine::min_ring_bytes(chunk_elems);
       })
       .def("staged_step", &PyEngine::staged_step, py::arg("pid"), py::arg("mode"), py::arg("p"),
            py::arg("g"), py::arg("host_grad"), py::arg("m"), py::arg("v"), py::arg("extra"),
@@ -373,6 +376,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("join_compute", &PyEngine::join_compute)
       .def("discard_prefetched", &PyEngine::discard_prefetched)
       .def("prefetched_chunks", &PyEngine::prefetched_chunks)
+      .def("prefetched_bytes", &PyEngine::prefetched_bytes)
+      .def("ring_bytes", &PyEngine::ring_bytes)
       .def("synchronize", &PyEngine::synchronize)
       .def("bytes_h2d", &PyEngine::bytes_h2d)
       .def("bytes_d2h", &PyEngine::bytes_d2h)

@@ -11,11 +11,13 @@ namespace {
 size_t elem_extra_bytes(int mode) {
   return mode == kModeFP32Master ? 4 : (mode == kModeSR ? 0 : 2);
 }
+size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 }  // namespace
 
-size_t OffloadEngine::workspace_bytes(const EngineOptions& opt) {
-  // g, m, v (bf16) + widest extra (fp32) per element
-  return (size_t)opt.slots * (size_t)opt.chunk_elems * 10;
+size_t OffloadEngine::min_ring_bytes(int64_t chunk_elems) {
+  // three full-width chunks (g, m, v, fp32 extra) so that load, compute and
+  // write-back of consecutive chunks overlap
+  return 3 * (up256(2 * chunk_elems) * 3 + up256(4 * chunk_elems));
 }
 
 void OffloadEngine::check(cudaError_t e, const char* what) {
@@ -27,113 +29,164 @@ OffloadEngine::OffloadEngine(int device, cudaStream_t compute, cudaStream_t h2d,
                              void* workspace, size_t ws_bytes, const EngineOptions& opt,
                              int n_tensors)
     : device_(device), compute_(compute), h2d_(h2d), d2h_(d2h), opt_(opt) {
-  if (opt_.chunk_elems % 8 != 0 || opt_.chunk_elems <= 0)
-    throw std::invalid_argument("OffloadEngine: chunk_elems must be a positive multiple of 8");
-  if (opt_.slots < 2) throw std::invalid_argument("OffloadEngine: need at least 2 slots");
-  if (ws_bytes < workspace_bytes(opt_))
-    throw std::invalid_argument("OffloadEngine: workspace too small");
-  slot_bytes_ = (size_t)opt_.chunk_elems * 10;
-  slots_.resize(opt_.slots);
-  for (int i = 0; i < opt_.slots; ++i) {
-    slots_[i].base = (char*)workspace + (size_t)i * slot_bytes_;
-    check(cudaEventCreateWithFlags(&slots_[i].h2d_done, cudaEventDisableTiming), "event");
-    check(cudaEventCreateWithFlags(&slots_[i].k_done, cudaEventDisableTiming), "event");
-    check(cudaEventCreateWithFlags(&slots_[i].free_ev, cudaEventDisableTiming), "event");
-  }
+  if (opt_.chunk_elems % 16 != 0 || opt_.chunk_elems <= 0)
+    throw std::invalid_argument("OffloadEngine: chunk_elems must be a positive multiple of 16");
+  if (ws_bytes < min_ring_bytes(opt_.chunk_elems))
+    throw std::invalid_argument("OffloadEngine: staging buffer smaller than min_ring_bytes(chunk_elems)");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    throw std::invalid_argument("OffloadEngine: staging buffer must be 256-byte aligned");
+  ring_ = static_cast<char*>(workspace);
+  ring_bytes_ = ws_bytes / 256 * 256;
   host_ready_.resize(n_tensors, nullptr);
   host_ready_set_.assign(n_tensors, 0);
-  for (auto& e : host_ready_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event");
   grad_ready_.resize(n_tensors, nullptr);
   grad_ready_set_.assign(n_tensors, 0);
+  for (auto& e : host_ready_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event");
   for (auto& e : grad_ready_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event");
   check(cudaEventCreateWithFlags(&tmp_ev_, cudaEventDisableTiming), "event");
   for (auto& e : join_ev_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event");
 }
 
 OffloadEngine::~OffloadEngine() {
-  for (auto& s : slots_) {
-    if (s.h2d_done) cudaEventDestroy(s.h2d_done);
-    if (s.k_done) cudaEventDestroy(s.k_done);
-    if (s.free_ev) cudaEventDestroy(s.free_ev);
-  }
+  for (auto& e : all_events_) cudaEventDestroy(e);
   for (auto& e : host_ready_) if (e) cudaEventDestroy(e);
   for (auto& e : grad_ready_) if (e) cudaEventDestroy(e);
   if (tmp_ev_) cudaEventDestroy(tmp_ev_);
   for (auto& e : join_ev_) if (e) cudaEventDestroy(e);
 }
 
-OffloadEngine::Slot& OffloadEngine::next_slot() {
-  // never hand out a slot that still holds prefetched, unconsumed state
-  if (!loaded_.empty() && loaded_.front() == cursor_) discard_prefetched();
-  Slot& s = slots_[cursor_];
-  cursor_ = (cursor_ + 1) % (int)slots_.size();
-  return s;
-}
-
-void OffloadEngine::load_chunk(Slot& s, const StagedStepArgs& a, int64_t off, int64_t len) {
-  const AdamStepArgs& k = a.k;
-  const int64_t C = opt_.chunk_elems;
-  const size_t xb = elem_extra_bytes(k.mode);
-  char* sg = s.base;
-  char* sm = s.base + 2 * C;
-  char* sv = s.base + 4 * C;
-  char* sx = s.base + 6 * C;
-  if (s.used) check(cudaStreamWaitEvent(h2d_, s.free_ev, 0), "wait slot");
-  if (a.host_grad) {
-    check(cudaMemcpyAsync(sg, (const char*)a.host_grad + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d g");
-    bytes_h2d_ += 2 * len;
+cudaEvent_t OffloadEngine::take_event() {
+  if (!pool_.empty()) {
+    cudaEvent_t e = pool_.back();
+    pool_.pop_back();
+    return e;
   }
-  check(cudaMemcpyAsync(sm, (const char*)k.m + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d m");
-  check(cudaMemcpyAsync(sv, (const char*)k.v + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d v");
-  bytes_h2d_ += 4 * len;
-  if (xb) {
-    check(cudaMemcpyAsync(sx, (const char*)k.extra + xb * off, xb * len, cudaMemcpyHostToDevice, h2d_), "h2d x");
-    bytes_h2d_ += xb * len;
-  }
-  check(cudaEventRecord(s.h2d_done, h2d_), "record");
-  s.used = true;
-  s.pid = a.pid;
-  s.off = off;
-  s.len = len;
-  s.has_grad = a.host_grad != nullptr;
+  cudaEvent_t e = nullptr;
+  check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event");
+  all_events_.push_back(e);
+  return e;
 }
 
 void OffloadEngine::discard_prefetched() {
+  // the chunks stay where they are until their space is needed; nothing reads them
+  for (Entry* e : loaded_) e->retired = true;
   loaded_.clear();
   inflight_.clear();
+  loaded_bytes_ = 0;
+}
+
+// Circular allocation.  Live chunks occupy the buffer in allocation order, so the
+// chunks a new allocation runs into are always the oldest ones; they can be evicted
+// once their write-back has been issued (the H2D stream then waits for it to finish).
+OffloadEngine::Entry* OffloadEngine::allocate(size_t bytes, bool may_discard) {
+  bytes = up256(bytes);
+  if (bytes > ring_bytes_) throw std::runtime_error("OffloadEngine: chunk larger than the staging buffer");
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    size_t start = head_;
+    bool wrapped = false;
+    if (start + bytes > ring_bytes_) { start = 0; wrapped = true; }
+    const size_t end = start + bytes;
+    auto overlaps = [&](const Entry& e) {
+      return (e.off < end && start < e.off + e.bytes) || (wrapped && e.off >= head_);
+    };
+    bool blocked = false;
+    for (const Entry& e : live_) {
+      if (!overlaps(e)) break;
+      if (!e.retired) { blocked = true; break; }
+    }
+    if (blocked) {
+      if (may_discard && !loaded_.empty()) { discard_prefetched(); continue; }
+      return nullptr;
+    }
+    while (!live_.empty() && overlaps(live_.front())) {
+      Entry& old = live_.front();
+      check(cudaStreamWaitEvent(h2d_, old.free_ev, 0), "wait for staging space");
+      for (auto it = inflight_.begin(); it != inflight_.end();)
+        it = (*it == &old) ? inflight_.erase(it) : it + 1;
+      pool_.push_back(old.h2d_done);
+      pool_.push_back(old.k_done);
+      pool_.push_back(old.free_ev);
+      live_.pop_front();
+    }
+    live_.emplace_back();
+    Entry& e = live_.back();
+    e.off = start;
+    e.bytes = bytes;
+    e.h2d_done = take_event();
+    e.k_done = take_event();
+    e.free_ev = take_event();
+    head_ = end;
+    return &e;
+  }
+  return nullptr;
+}
+
+void OffloadEngine::wait_host_copy(const StagedStepArgs& a) {
+  // the host copy must be complete: the previous write-back of this tensor
+  if (a.pid >= 0 && a.pid < (int)host_ready_.size() && host_ready_set_[a.pid])
+    check(cudaStreamWaitEvent(h2d_, host_ready_[a.pid], 0), "wait host_ready");
+  if (a.host_grad && a.pid >= 0 && a.pid < (int)grad_ready_.size() && grad_ready_set_[a.pid])
+    check(cudaStreamWaitEvent(h2d_, grad_ready_[a.pid], 0), "wait grad_ready");
+}
+
+OffloadEngine::Entry* OffloadEngine::load_chunk(const StagedStepArgs& a, int64_t off, int64_t len,
+                                                bool may_discard) {
+  const AdamStepArgs& k = a.k;
+  const size_t xb = elem_extra_bytes(k.mode);
+  const size_t gb = a.host_grad ? up256(2 * len) : 0;
+  const size_t sb = up256(2 * len);
+  Entry* e = allocate(gb + 2 * sb + up256(xb * len), may_discard);
+  if (e == nullptr) return nullptr;
+  char* base = ring_ + e->off;
+  e->g = base;
+  e->m = base + gb;
+  e->v = e->m + sb;
+  e->x = e->v + sb;
+  if (a.host_grad) {
+    check(cudaMemcpyAsync(e->g, (const char*)a.host_grad + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d g");
+    bytes_h2d_ += 2 * len;
+  }
+  check(cudaMemcpyAsync(e->m, (const char*)k.m + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d m");
+  check(cudaMemcpyAsync(e->v, (const char*)k.v + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d v");
+  bytes_h2d_ += 4 * len;
+  if (xb) {
+    check(cudaMemcpyAsync(e->x, (const char*)k.extra + xb * off, xb * len, cudaMemcpyHostToDevice, h2d_), "h2d x");
+    bytes_h2d_ += xb * len;
+  }
+  check(cudaEventRecord(e->h2d_done, h2d_), "record");
+  e->pid = a.pid;
+  e->eoff = off;
+  e->len = len;
+  e->has_grad = a.host_grad != nullptr;
+  return e;
 }
 
 int64_t OffloadEngine::prefetch(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks,
-                                int max_inflight) {
+                                int max_inflight, bool* full) {
   const AdamStepArgs& k = a.k;
   const int64_t C = opt_.chunk_elems;
-  int64_t off = from_off;
+  int64_t off = from_off, issued = 0;
   bool waited = false;
-  int64_t issued = 0;
-  while (off < k.n && (int)loaded_.size() < (int)slots_.size() - 1 &&
-         (max_chunks <= 0 || issued < max_chunks)) {
+  if (full) *full = false;
+  while (off < k.n && (max_chunks <= 0 || issued < max_chunks)) {
     if (max_inflight > 0) {
-      while (!inflight_.empty() && cudaEventQuery(slots_[inflight_.front()].h2d_done) == cudaSuccess)
+      while (!inflight_.empty() && cudaEventQuery(inflight_.front()->h2d_done) == cudaSuccess)
         inflight_.pop_front();
       (void)cudaGetLastError();  // cudaErrorNotReady is not an error
       if ((int)inflight_.size() >= max_inflight) break;
     }
-    ++issued;
-    if (!waited) {
-      // the host copy must be complete: previous step's write-back of this tensor
-      if (a.pid >= 0 && a.pid < (int)host_ready_.size() && host_ready_set_[a.pid])
-        check(cudaStreamWaitEvent(h2d_, host_ready_[a.pid], 0), "wait host_ready");
-      if (a.host_grad && a.pid >= 0 && a.pid < (int)grad_ready_.size() && grad_ready_set_[a.pid])
-        check(cudaStreamWaitEvent(h2d_, grad_ready_[a.pid], 0), "wait grad_ready");
-      waited = true;
-    }
+    if (!waited) { wait_host_copy(a); waited = true; }
     const int64_t len = (k.n - off < C) ? (k.n - off) : C;
-    const int idx = cursor_;
-    Slot& s = next_slot();
-    load_chunk(s, a, off, len);
-    loaded_.push_back(idx);
-    if (max_inflight > 0) inflight_.push_back(idx);
+    Entry* e = load_chunk(a, off, len, /*may_discard=*/false);
+    if (e == nullptr) {
+      if (full) *full = true;
+      break;
+    }
+    loaded_.push_back(e);
+    loaded_bytes_ += e->bytes;
+    if (max_inflight > 0) inflight_.push_back(e);
     off += len;
+    ++issued;
   }
   return off;
 }
@@ -145,58 +198,49 @@ void OffloadEngine::staged_step(const StagedStepArgs& a) {
   bool waited = false;
   for (int64_t off = 0; off < k.n; off += C) {
     const int64_t len = (k.n - off < C) ? (k.n - off) : C;
-    Slot* sp = nullptr;
+    Entry* e = nullptr;
     if (!loaded_.empty()) {
-      Slot& f = slots_[loaded_.front()];
-      if (f.pid == a.pid && f.off == off && f.len == len && f.has_grad == (a.host_grad != nullptr)) {
-        sp = &f;  // already on its way: prefetched
+      Entry* f = loaded_.front();
+      if (f->pid == a.pid && f->eoff == off && f->len == len && f->has_grad == (a.host_grad != nullptr)) {
+        e = f;  // already on its way: prefetched
         loaded_.pop_front();
+        loaded_bytes_ -= e->bytes;
       } else {
-        discard_prefetched();  // out-of-order step: give the slots back
+        discard_prefetched();  // out-of-order step: give the space back
       }
     }
-    if (sp == nullptr) {
-      if (!waited) {
-        if (a.pid >= 0 && a.pid < (int)host_ready_.size() && host_ready_set_[a.pid])
-          check(cudaStreamWaitEvent(h2d_, host_ready_[a.pid], 0), "wait host_ready");
-        if (a.host_grad && a.pid >= 0 && a.pid < (int)grad_ready_.size() && grad_ready_set_[a.pid])
-          check(cudaStreamWaitEvent(h2d_, grad_ready_[a.pid], 0), "wait grad_ready");
-        waited = true;
-      }
-      sp = &next_slot();
-      load_chunk(*sp, a, off, len);
+    if (e == nullptr) {
+      if (!waited) { wait_host_copy(a); waited = true; }
+      e = load_chunk(a, off, len, /*may_discard=*/true);
+      if (e == nullptr) throw std::runtime_error("OffloadEngine: staging buffer exhausted");
     }
-    Slot& s = *sp;
-    char* sg = s.base;
-    char* sm = s.base + 2 * C;
-    char* sv = s.base + 4 * C;
-    char* sx = s.base + 6 * C;
-    check(cudaStreamWaitEvent(compute_, s.h2d_done, 0), "wait h2d");
+    check(cudaStreamWaitEvent(compute_, e->h2d_done, 0), "wait h2d");
 
     AdamStepArgs c = k;
     c.n = len;
     c.elem_offset = k.elem_offset + off;
     c.p = k.p ? (char*)k.p + 2 * off : nullptr;
     if (k.n_g_peers > 0) { c.g = nullptr; c.g2 = nullptr; }
-    else if (k.g && a.host_grad) { c.g = (const char*)k.g + 2 * off; c.g2 = sg; }
+    else if (k.g && a.host_grad) { c.g = (const char*)k.g + 2 * off; c.g2 = e->g; }
     else if (k.g) { c.g = (const char*)k.g + 2 * off; c.g2 = nullptr; }
-    else { c.g = sg; c.g2 = nullptr; }
-    c.m = sm; c.v = sv; c.extra = xb ? sx : nullptr;
+    else { c.g = e->g; c.g2 = nullptr; }
+    c.m = e->m; c.v = e->v; c.extra = xb ? e->x : nullptr;
     c.max_ctas = opt_.max_ctas;
     for (int j = 0; j < k.n_g_peers; ++j) c.g_peers[j] = (const char*)k.g_peers[j] + 2 * off;
     for (int j = 0; j < k.n_p_peers; ++j) c.p_peers[j] = (char*)k.p_peers[j] + 2 * off;
     check(launch_adam_step(c, compute_), "adam_step");
-    check(cudaEventRecord(s.k_done, compute_), "record");
-    check(cudaStreamWaitEvent(d2h_, s.k_done, 0), "wait k");
+    check(cudaEventRecord(e->k_done, compute_), "record");
+    check(cudaStreamWaitEvent(d2h_, e->k_done, 0), "wait k");
 
-    check(cudaMemcpyAsync((char*)k.m + 2 * off, sm, 2 * len, cudaMemcpyDeviceToHost, d2h_), "d2h m");
-    check(cudaMemcpyAsync((char*)k.v + 2 * off, sv, 2 * len, cudaMemcpyDeviceToHost, d2h_), "d2h v");
+    check(cudaMemcpyAsync((char*)k.m + 2 * off, e->m, 2 * len, cudaMemcpyDeviceToHost, d2h_), "d2h m");
+    check(cudaMemcpyAsync((char*)k.v + 2 * off, e->v, 2 * len, cudaMemcpyDeviceToHost, d2h_), "d2h v");
     bytes_d2h_ += 4 * len;
     if (xb) {
-      check(cudaMemcpyAsync((char*)k.extra + xb * off, sx, xb * len, cudaMemcpyDeviceToHost, d2h_), "d2h x");
+      check(cudaMemcpyAsync((char*)k.extra + xb * off, e->x, xb * len, cudaMemcpyDeviceToHost, d2h_), "d2h x");
       bytes_d2h_ += xb * len;
     }
-    check(cudaEventRecord(s.free_ev, d2h_), "record");
+    check(cudaEventRecord(e->free_ev, d2h_), "record");
+    e->retired = true;
   }
   if (a.pid >= 0 && a.pid < (int)host_ready_.size()) {
     check(cudaEventRecord(host_ready_[a.pid], d2h_), "record host_ready");
@@ -225,15 +269,15 @@ void OffloadEngine::staged_grad_to_host(int pid, void* host_grad, const void* de
   bool first_chunk = true;
   for (int64_t off = 0; off < n; off += C) {
     const int64_t len = (n - off < C) ? (n - off) : C;
-    Slot& s = next_slot();
-    char* sg = s.base;
-    if (s.used) check(cudaStreamWaitEvent(h2d_, s.free_ev, 0), "wait slot");
+    Entry* e = allocate(2 * len, /*may_discard=*/true);
+    if (e == nullptr) throw std::runtime_error("OffloadEngine: staging buffer exhausted");
+    char* sg = ring_ + e->off;
     if (!first) {
       check(cudaMemcpyAsync(sg, (const char*)host_grad + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d g");
       bytes_h2d_ += 2 * len;
     }
-    check(cudaEventRecord(s.h2d_done, h2d_), "record");
-    check(cudaStreamWaitEvent(compute_, s.h2d_done, 0), "wait h2d");
+    check(cudaEventRecord(e->h2d_done, h2d_), "record");
+    check(cudaStreamWaitEvent(compute_, e->h2d_done, 0), "wait h2d");
     AccumArgs acc;
     acc.out = sg;
     acc.a = (const char*)dev_grad + 2 * off;
@@ -244,12 +288,12 @@ void OffloadEngine::staged_grad_to_host(int pid, void* host_grad, const void* de
     acc.scratch = scratch;
     acc.max_ctas = opt_.max_ctas;
     check(launch_grad_accumulate(acc, compute_), "grad_accumulate");
-    check(cudaEventRecord(s.k_done, compute_), "record");
-    check(cudaStreamWaitEvent(d2h_, s.k_done, 0), "wait k");
+    check(cudaEventRecord(e->k_done, compute_), "record");
+    check(cudaStreamWaitEvent(d2h_, e->k_done, 0), "wait k");
     check(cudaMemcpyAsync((char*)host_grad + 2 * off, sg, 2 * len, cudaMemcpyDeviceToHost, d2h_), "d2h g");
     bytes_d2h_ += 2 * len;
-    check(cudaEventRecord(s.free_ev, d2h_), "record");
-    s.used = true;
+    check(cudaEventRecord(e->free_ev, d2h_), "record");
+    e->retired = true;
     first_chunk = false;
   }
   if (tracked) {

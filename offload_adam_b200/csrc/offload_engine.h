@@ -3,11 +3,14 @@
 // Two ways of moving state through the step are provided; both run entirely on
 // side streams so that they overlap the rest of backward:
 //
-//  * staged: each tensor is cut into fixed-size chunks that flow through a
-//    ring of device slots: H2D (copy stream A) -> kernel (compute stream) ->
-//    D2H (copy stream B).  Three chunks are in flight at any time, so both DMA
-//    directions and the SMs work concurrently and device memory use is bounded
-//    by slots * chunk bytes, independent of tensor size.
+//  * staged: each tensor is cut into chunks that flow through a byte-addressed
+//    circular staging buffer in device memory: H2D (copy stream A) -> kernel
+//    (compute stream) -> D2H (copy stream B).  Many chunks are in flight at any
+//    time, so both DMA directions and the SMs work concurrently, and device memory
+//    use is bounded by the size of the buffer, independent of tensor size.  A
+//    chunk takes exactly the bytes it needs, so small tensors waste nothing.
+//    The same buffer holds state brought in ahead of its step (prefetch) and state
+//    whose write-back is still draining after the step.
 //  * zero-copy: the kernel reads and writes the mapped host buffers itself; no
 //    staging memory at all (see adam_step.h).  Issued directly by the caller.
 //
@@ -20,6 +23,7 @@
 #include <stdint.h>
 
 #include <deque>
+#include <list>
 #include <vector>
 
 #include "adam_step.h"
@@ -27,8 +31,7 @@
 namespace oab {
 
 struct EngineOptions {
-  int64_t chunk_elems = int64_t(8) << 20;  // elements per staged chunk
-  int slots = 4;                           // ring depth
+  int64_t chunk_elems = int64_t(8) << 20;  // largest chunk, in elements
   int max_ctas = 0;                        // grid cap for kernels on the compute stream
 };
 
@@ -43,73 +46,84 @@ struct StagedStepArgs {
 
 class OffloadEngine {
  public:
-  // `workspace` must hold workspace_bytes(opt) of device memory.
+  // `workspace` is the staging buffer: workspace_bytes of device memory, 256-byte
+  // aligned, at least min_ring_bytes(opt.chunk_elems).
   OffloadEngine(int device, cudaStream_t compute, cudaStream_t h2d, cudaStream_t d2h,
                 void* workspace, size_t workspace_bytes, const EngineOptions& opt, int n_tensors);
   ~OffloadEngine();
-  static size_t workspace_bytes(const EngineOptions& opt);
+  // Smallest staging buffer that can pipeline chunks of `chunk_elems` elements.
+  static size_t min_ring_bytes(int64_t chunk_elems);
 
-  // Adam step of one tensor through the slot ring.  The caller has already made
-  // the compute stream wait for the gradient producer.  Chunks that prefetch()
-  // already brought in are consumed in place.
+  // Adam step of one tensor through the staging buffer.  The caller has already
+  // made the compute stream wait for the gradient producer.  Chunks that
+  // prefetch() already brought in are consumed in place.
   void staged_step(const StagedStepArgs& a);
 
-  // Early H2D: copies the host state (and host gradient, if given) of the tensor into
-  // free slots, chunk by chunk from `from_off`, before its gradient exists.  Stops when
-  // the ring is full.  Returns the element offset up to which the tensor is now loaded
-  // (== n when complete).  Only the pid, mode, n and host pointers of `a` are used.
-  // Tensors must later be stepped in the order they were prefetched; a step that finds
-  // other chunks at the head of the queue discards them (their H2D is wasted, nothing
-  // else).
-  // At most `max_chunks` chunks are issued per call (<= 0: no limit), so that callers can
-  // pace the bulk copies and leave gaps in the copy-engine queue for other traffic.
-  // With max_inflight > 0 a chunk is issued only while fewer than that many earlier
-  // prefetch copies are still running (checked with cudaEventQuery, never blocking), which
-  // bounds how long somebody else's H2D copy can wait behind ours.
-  int64_t prefetch(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks, int max_inflight = 0);
+  // Early H2D: copies the host state (and host gradient, if given) of the tensor
+  // into free staging space, chunk by chunk from `from_off`, before its gradient
+  // exists.  Stops when the buffer is full, after `max_chunks` chunks (<= 0: no limit)
+  // or, with max_inflight > 0, while that many earlier prefetch copies are still
+  // running (checked with cudaEventQuery, never blocking), which bounds how long
+  // somebody else's H2D copy can wait behind ours.  Returns the element offset up to
+  // which the tensor is now loaded (== n when complete); *full is set when the buffer
+  // could not take the next chunk.  Only the pid, mode, n and host pointers of `a` are
+  // used.  Tensors must later be stepped in the order they were prefetched; a step
+  // that finds other chunks at the head of the queue discards them (their H2D is
+  // wasted, nothing else).
+  int64_t prefetch(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks, int max_inflight,
+                   bool* full);
   int64_t prefetched_chunks() const { return (int64_t)loaded_.size(); }
+  int64_t prefetched_bytes() const { return (int64_t)loaded_bytes_; }
   void discard_prefetched();
 
-  // Makes `stream` wait for the kernels enqueued so far (parameters are updated) but
-  // not for the trailing D2H write-backs of the state.
-  void join_compute(cudaStream_t stream);
-
-  // host_grad (+)= dev_grad through the ring, optionally producing sum of squares of
+  // host_grad (+)= dev_grad through the buffer, optionally producing sum of squares of
   // the result into *sumsq_out (device pointer).  first == true: plain D2H copy.
   void staged_grad_to_host(int pid, void* host_grad, const void* dev_grad, int64_t n, bool first,
                            float* sumsq_out, float* scratch);
 
   // Makes `stream` wait until every transfer/kernel enqueued so far has finished.
   void join(cudaStream_t stream);
+  // Makes `stream` wait for the kernels enqueued so far (parameters are updated) but
+  // not for the trailing D2H write-backs of the state.
+  void join_compute(cudaStream_t stream);
   // Blocks the host until the engine streams are idle.
   void synchronize();
 
   int64_t bytes_h2d() const { return bytes_h2d_; }
   int64_t bytes_d2h() const { return bytes_d2h_; }
   void reset_counters() { bytes_h2d_ = bytes_d2h_ = 0; }
+  size_t ring_bytes() const { return ring_bytes_; }
 
  private:
-  struct Slot {
-    char* base = nullptr;
+  // One chunk resident in the staging buffer.
+  struct Entry {
+    size_t off = 0, bytes = 0;  // placement in the buffer
     cudaEvent_t h2d_done = nullptr, k_done = nullptr, free_ev = nullptr;
-    bool used = false;
-    // prefetched content, valid while the slot is queued in loaded_
+    bool retired = false;  // its D2H has been issued (or it was discarded): the memory may
+                           // be reused once free_ev has fired
+    // content, for prefetched chunks
     int pid = -1;
-    int64_t off = 0, len = 0;
+    int64_t eoff = 0, len = 0;
     bool has_grad = false;
+    char *g = nullptr, *m = nullptr, *v = nullptr, *x = nullptr;  // sub-buffers
   };
-  Slot& next_slot();
-  void load_chunk(Slot& s, const StagedStepArgs& a, int64_t off, int64_t len);
+  Entry* allocate(size_t bytes, bool may_discard);
+  Entry* load_chunk(const StagedStepArgs& a, int64_t off, int64_t len, bool may_discard);
+  cudaEvent_t take_event();
+  void wait_host_copy(const StagedStepArgs& a);
   void check(cudaError_t e, const char* what);
 
   int device_;
   cudaStream_t compute_, h2d_, d2h_;
   EngineOptions opt_;
-  std::vector<Slot> slots_;
-  size_t slot_bytes_ = 0;
-  int cursor_ = 0;
-  std::deque<int> loaded_;  // slots filled by prefetch(), in consumption order
-  std::deque<int> inflight_;  // prefetch copies possibly still running (slot indices)
+  char* ring_ = nullptr;
+  size_t ring_bytes_ = 0, head_ = 0;
+  std::list<Entry> live_;        // allocation order, oldest first
+  std::deque<Entry*> loaded_;    // prefetched, not yet consumed (consumption order)
+  std::deque<Entry*> inflight_;  // prefetch copies possibly still running
+  size_t loaded_bytes_ = 0;
+  std::vector<cudaEvent_t> pool_;
+  std::vector<cudaEvent_t> all_events_;
   std::vector<cudaEvent_t> host_ready_;  // per tensor: last D2H of its state finished
   std::vector<char> host_ready_set_;
   std::vector<cudaEvent_t> grad_ready_;  // per tensor: last D2H of its host gradient finished

@@ -62,16 +62,18 @@ class TransferEngine:
                 self.d2h_stream = torch.cuda.Stream()
                 self.scratch = grad_ops.sumsq_scratch(self.device)
                 if transfer == "staged":
-                    # the ring doubles as the early-H2D / trailing-D2H staging area
-                    ring_slots = max(int(ring_slots), min(1024, int(staging_bytes) // (int(chunk_elems) * 10)))
-                    self.ring_slots = ring_slots
-                    self.staging_bytes = ring_slots * int(chunk_elems) * 10
-                    nbytes = self.C.OffloadEngine.workspace_bytes(chunk_elems, ring_slots)
+                    # circular staging buffer: pipelines the chunks of a step and doubles as
+                    # the early-H2D / trailing-D2H area
+                    chunk_elems = max(16, int(chunk_elems) // 16 * 16)
+                    floor = self.C.OffloadEngine.min_ring_bytes(chunk_elems)
+                    nbytes = max(floor, int(ring_slots) * chunk_elems * 10, int(staging_bytes))
+                    nbytes = (nbytes + 255) // 256 * 256
                     ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+                    self.staging_bytes = nbytes
                     self._native = self.C.OffloadEngine(
                         self.device.index or 0, self.opt_stream.cuda_stream,
                         self.h2d_stream.cuda_stream, self.d2h_stream.cuda_stream, ws,
-                        chunk_elems, ring_slots, self.max_ctas, n_tensors,
+                        chunk_elems, self.max_ctas, n_tensors,
                     )
 
     # ------------------------------------------------------------ stream glue
@@ -104,18 +106,16 @@ class TransferEngine:
     def prefetch(self, pid, states, host_grad=None, from_off=0, max_chunks=0, max_inflight=0):
         """Start the H2D of a tensor's state ahead of its step (staged transfer only),
         at most ``max_chunks`` chunks of it (0: as many as fit).  Returns
-        ``(offset, issued)``: the element offset up to which the tensor is loaded and the
-        number of chunks this call issued.  ``max_inflight`` > 0 issues nothing while that
+        ``(offset, full)``: the element offset up to which the tensor is loaded and
+        whether the staging buffer refused the next chunk.  ``max_inflight`` > 0 issues nothing while that
         many earlier prefetch copies are still running."""
         n = states["exp_avg"].numel()
         if self._native is None:
-            return n, 0
+            return n, False
         extra = states.get("master_params", states.get("rounding_error"))
-        before = self._native.prefetched_chunks()
-        off = self._native.prefetch(pid, self.mode_id, host_grad, states["exp_avg"],
-                                    states["exp_avg_sq"], extra, int(from_off), int(max_chunks),
-                                    int(max_inflight))
-        return off, self._native.prefetched_chunks() - before
+        return self._native.prefetch(pid, self.mode_id, host_grad, states["exp_avg"],
+                                     states["exp_avg_sq"], extra, int(from_off), int(max_chunks),
+                                     int(max_inflight))
 
     def synchronize(self):
         if self.cuda:

@@ -94,7 +94,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             accumulators (default: a quarter of the device's memory).
         chunk_elems: elements per staged chunk (default 8 Mi divided by the world size,
             at least 1 Mi).
-        staging_bytes: HBM set aside for the slot ring of the staged transfer
+        staging_bytes: HBM set aside for the circular staging buffer of the staged transfer
             (default 8 GiB, capped at this rank's state size; about what the reference
             keeps on the GPU as whole state tensors in flight: two of the 4.2 GB
             embedding-sized states of an 8B model).  State of the first tensors of the next step is brought
@@ -552,28 +552,23 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         if order is None:
             return
         eng = self._engine
-        while max_chunks > 0:
-            if self._pf_idx >= len(order):
-                self._pf_order = None
-                return
-            p = order[self._pf_idx]
-            if p in self._quant_params:
-                self._pf_order = None  # takes its own route through a device temporary
-                return
-            st = self.state[p]
-            states = {k: st[k] for k in self._non_grad_keys}
-            n = states["exp_avg"].numel()
-            before = eng._native.prefetched_chunks()
-            off, issued = eng.prefetch(self._pid[p], states, None, self._pf_off, max_chunks, max_inflight=1)
-            max_chunks -= issued
-            if off >= n:
-                self._pf_idx += 1
-                self._pf_off = 0
-            else:
-                self._pf_off = off
-                if before + issued >= eng.ring_slots - 1:
-                    self._pf_order = None  # ring is full
-                return  # budget used up, or an earlier copy is still in flight: try later
+        if self._pf_idx >= len(order):
+            self._pf_order = None
+            return
+        p = order[self._pf_idx]
+        if p in self._quant_params:
+            self._pf_order = None  # takes its own route through a device temporary
+            return
+        st = self.state[p]
+        states = {k: st[k] for k in self._non_grad_keys}
+        off, full = eng.prefetch(self._pid[p], states, None, self._pf_off, max_chunks, max_inflight=1)
+        if full:
+            self._pf_order = None  # no staging space left for this step
+        elif off >= states["exp_avg"].numel():
+            self._pf_idx += 1
+            self._pf_off = 0
+        else:
+            self._pf_off = off  # an earlier copy is still in flight, or the budget is used up
 
     def _finish_step(self):
         """Run what the hooks deferred and make the main stream wait for the side
@@ -602,8 +597,10 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             self._finish_step()
             return
         if self.verbose > 1 and self._engine.can_prefetch:
-            print(f"{self._log_prefix()}step: {self._engine._native.prefetched_chunks()} chunk(s) of "
-                  f"{self._engine.ring_slots} slots prefetched", flush=True)
+            nat = self._engine._native
+            print(f"{self._log_prefix()}step: {nat.prefetched_chunks()} chunk(s), "
+                  f"{nat.prefetched_bytes() / 2**30:.2f} of {nat.ring_bytes() / 2**30:.2f} GiB of staging "
+                  f"hold prefetched state", flush=True)
         clip = self._global_clip_coef()
         inplace = []
         for group in self.param_groups:
