@@ -491,11 +491,17 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             g = dev_grad if dev_grad is not None else host_grad
             g2 = host_grad if dev_grad is not None else None
             states["grad"] = g
+            # formats with a per-tensor scale get max|master| as a by-product of the step
+            amax = torch.zeros(1, dtype=torch.float32, device=self.device) \
+                if getattr(p.data, "USES_TENSOR_AMAX", False) else None
             adam_step(self.mode, None, states, *self._hp(group), st["step"],
                       decoupled_weight_decay=self.decoupled_weight_decay, clip_coef=clip_coef,
-                      grad2=g2, max_ctas=eng.max_ctas, stream=eng.opt_stream.cuda_stream,
+                      grad2=g2, amax=amax, max_ctas=eng.max_ctas, stream=eng.opt_stream.cuda_stream,
                       use_cuda=True)
-            p.data.copy_(master)
+            if amax is not None:
+                p.data._quantize_into(master, amax)
+            else:
+                p.data.copy_(master)
             st["master_params"].copy_(master, non_blocking=True)
         eng._retain(dev_grad)
 

@@ -260,26 +260,59 @@ class DistributedOffloadAdam(OffloadAdam):
     def _step_quant(self, p, group, st, dev_grad, host_grad, clip_coef):
         if p not in self._sharded:
             return super()._step_quant(p, group, st, dev_grad, host_grad, clip_coef)
-        # sharded quantized parameter: update the master slice, gather the full fp32
-        # master and let every replica re-quantize it
+        # sharded quantized parameter: the owner of each row range updates its master
+        # slice, quantizes those rows and the PACKED rows are gathered (at most one byte
+        # per element on the wire instead of four, and no replica re-quantizes rows it
+        # does not own).  The reference gathers the fp32 master and re-quantizes the whole
+        # weight on every rank (src/offload_adam/offload_adam.py:893-921).
         eng = self._engine
         from ..ops.adam_step import adam_step
 
+        q = p.data
+        lo, hi = self._rows(p)
         eng.fork_from_main()
         with self._side():
             master = st["master_params"].to(self.device, non_blocking=True) if self._cuda \
                 else st["master_params"]
             states = {"grad": dev_grad, "exp_avg": st["exp_avg"], "exp_avg_sq": st["exp_avg_sq"],
                       "master_params": master}
+            amax = torch.zeros(1, dtype=torch.float32, device=master.device) if q.USES_TENSOR_AMAX else None
             adam_step(self.mode, None, states, *self._hp(group), st["step"],
-                      decoupled_weight_decay=self.decoupled_weight_decay, clip_coef=clip_coef,
+                      decoupled_weight_decay=self.decoupled_weight_decay, clip_coef=clip_coef, amax=amax,
                       max_ctas=eng.max_ctas, stream=self._opt_stream_handle(), use_cuda=self._cuda)
-            full = torch.empty(p.shape, dtype=torch.float32, device=self.device)
-            self._all_gather_rows(full, master)
-            p.data.copy_(full)
+            if amax is not None:
+                dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=self._pg)
+            shard, views = q.row_shard(lo, hi)
+            shard._quantize_into(master, amax)
+            for full, view, part in zip(q._payload(), views, shard._payload()):
+                if view.shape == full.shape:
+                    continue  # per-tensor quantity: every rank wrote the same value
+                self._gather_payload(full, view, part)
             if self._cuda:
                 st["master_params"].copy_(master, non_blocking=True)
         eng._retain(dev_grad)
+
+    def _gather_payload(self, full, view, part):
+        """All-gather one packed payload tensor from per-rank row ranges."""
+        if part.data_ptr() == view.data_ptr():
+            # row-major payload: ranks own consecutive byte ranges of ``full``; in place
+            flat = full.view(-1)
+            mine = part.view(-1)
+            if flat.element_size() == 1:
+                flat, mine = flat.view(torch.uint8), mine.view(torch.uint8)
+            if full.is_cuda:
+                dist.all_gather_into_tensor(flat, mine, group=self._pg)
+            else:
+                parts = [torch.empty_like(mine) for _ in range(self._world_size)]
+                dist.all_gather(parts, mine.clone(), group=self._pg)
+                flat.copy_(torch.cat(parts))
+            return
+        # transposed payload (rows of the weight are columns here): gather the
+        # contiguous temporaries and lay them side by side
+        dim = next(d for d in range(full.dim()) if view.shape[d] != full.shape[d])
+        parts = [torch.empty_like(part) for _ in range(self._world_size)]
+        dist.all_gather(parts, part, group=self._pg)
+        torch.cat(parts, dim=dim, out=full)
 
     def _global_clip_coef(self):
         if self.max_grad_norm is None:

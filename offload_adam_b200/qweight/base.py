@@ -133,9 +133,35 @@ class QWeightBase(Tensor):
         """Dense reconstruction at ``dtype`` (default: the outer dtype)."""
         raise NotImplementedError
 
-    def _quantize_into(self, src: Tensor) -> None:
-        """Re-quantize dense ``src`` into this instance's payload tensors."""
+    def _quantize_into(self, src: Tensor, amax: Optional[Tensor] = None) -> None:
+        """Re-quantize dense ``src`` into this instance's payload tensors.  ``amax``
+        (a one-element fp32 tensor holding max|x| of the WHOLE weight) is used by
+        formats with a per-tensor scale and ignored by the others."""
         raise NotImplementedError
+
+    #: True when quantization needs max|x| over the whole tensor (a per-tensor scale)
+    USES_TENSOR_AMAX = False
+
+    def _payload_rows(self, lo: int, hi: int):
+        """Per payload tensor, the view that holds output rows ``[lo, hi)`` of the
+        weight (the whole tensor for per-tensor quantities)."""
+        raise NotImplementedError
+
+    def row_shard(self, lo: int, hi: int):
+        """A weight over output rows ``[lo, hi)`` for sharded re-quantization.
+
+        Returns ``(shard, views)``.  ``views[i]`` is where rows ``[lo, hi)`` live in
+        payload tensor ``i`` of ``self``.  The shard's payload aliases those views
+        when they are contiguous (row-major formats), otherwise it owns contiguous
+        temporaries of the same shape (GPTQ's transposed layout) that the caller
+        copies or gathers into place.  Quantizing rows separately gives the same
+        bits as quantizing the whole weight because no block or group of any format
+        spans two output rows; the per-tensor scale of NVFP4 is the exception and
+        is handled by passing the global ``amax``."""
+        views = self._payload_rows(lo, hi)
+        payload = [v if v.is_contiguous() else torch.empty(v.shape, dtype=v.dtype, device=v.device)
+                   for v in views]
+        return self._rebuild(payload), views
 
     def _with_outer_dtype(self, payload, dtype):
         """Rebuild with a different outer dtype (used by ``.to(dtype)``)."""
@@ -204,7 +230,7 @@ def _install_common_handlers(cls):
             for d, s in zip(dst._payload(), src._payload()):
                 d.copy_(s)
         elif isinstance(dst, cls):
-            dst._quantize_into(src)
+            dst._quantize_into(src, None)
         else:
             dst.copy_(src.dequantize())
         return dst

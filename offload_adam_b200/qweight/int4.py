@@ -125,7 +125,11 @@ class Int4QWeight(QWeightBase):
         out = (vals * self.scales.T.to(work).unsqueeze(-1)).reshape(self.shape)
         return out if dtype is None else out.to(dtype)
 
-    def _quantize_into(self, src: Tensor) -> None:
+    def _payload_rows(self, lo, hi):
+        # GPTQ stores (in, out): output rows are columns of both tensors
+        return [self.qweight[:, lo:hi], self.scales[:, lo:hi]]
+
+    def _quantize_into(self, src: Tensor, amax=None) -> None:
         if src.dtype in _CUDA_DTYPES and self.scales.dtype in _CUDA_DTYPES and \
                 _kernel_ok(self.shape[1], self.group_size, self.qweight, src):
             _quantize_pack_int4_cuda(src, self.group_size, self.scales.dtype, self.qweight, self.scales)

@@ -98,7 +98,10 @@ class Int8QWeight(QWeightBase):
         out = self.weight.to(work) * self.scales.to(work).unsqueeze(1)
         return out if dtype is None else out.to(dtype)
 
-    def _quantize_into(self, src: Tensor) -> None:
+    def _payload_rows(self, lo, hi):
+        return [self.weight[lo:hi], self.scales[lo:hi]]
+
+    def _quantize_into(self, src: Tensor, amax=None) -> None:
         if self.weight.is_cuda and src.is_cuda and src.dtype in _CUDA_DTYPES and self.scales.dtype in _CUDA_DTYPES:
             _quantize_int8_cuda(src, self.scales.dtype, self.weight, self.scales)
             return

@@ -143,7 +143,11 @@ class NF4QWeight(QWeightBase):
             return _dequant_nf4_cuda(self.weight_packed, self.absmax, self.in_f, self.blocksize, dtype)
         return dequantize_nf4_blockwise(self.weight_packed, self.absmax, self.in_f, self.blocksize, dtype)
 
-    def _quantize_into(self, src: Tensor) -> None:
+    def _payload_rows(self, lo, hi):
+        per_row = self.in_f // self.blocksize
+        return [self.weight_packed[lo:hi], self.absmax[lo * per_row:hi * per_row]]
+
+    def _quantize_into(self, src: Tensor, amax=None) -> None:
         if src.is_cuda and _kernel_ok(self.weight_packed, self.blocksize, src.dtype):
             _quantize_nf4_cuda(src, self.blocksize, self.weight_packed, self.absmax)
             return

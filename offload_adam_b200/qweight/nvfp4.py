@@ -62,12 +62,13 @@ def _quantize_fp4_e2m1_rne(x: Tensor) -> Tensor:
     return code | (torch.signbit(x).to(torch.uint8) << 3)
 
 
-def _scales(t: Tensor, eps: float):
+def _scales(t: Tensor, eps: float, amax=None):
     """Shared head of the quantizer: tensor scale, per-block e4m3 scale and the
-    reciprocal of the effective scale."""
+    reciprocal of the effective scale.  ``amax`` overrides max|t| (row shards of a
+    larger weight pass the whole weight's)."""
     out_f, in_f = t.shape
     groups = in_f // NVFP4_BLOCKSIZE
-    amax = t.abs().amax().clamp(min=eps)
+    amax = (t.abs().amax() if amax is None else amax.to(t.device, torch.float32).reshape(())).clamp(min=eps)
     global_scale = amax / (FP8_E4M3_MAX * FP4_E2M1_MAX)
     inv_global = 1.0 / global_scale.clamp(min=eps)
     blocks = t.reshape(out_f, groups, NVFP4_BLOCKSIZE)
@@ -78,12 +79,12 @@ def _scales(t: Tensor, eps: float):
 
 
 @torch.no_grad()
-def quantize_nvfp4_blockwise(tensor: Tensor, eps: float = _EPS) -> Tuple[Tensor, Tensor, Tensor]:
+def quantize_nvfp4_blockwise(tensor: Tensor, eps: float = _EPS, amax=None) -> Tuple[Tensor, Tensor, Tensor]:
     """PyTorch restatement of the NVFP4 quantizer.  ``in_f % 16 == 0`` required.
     Returns ``(weight_packed, block_scale_fp8, global_scale)``."""
     assert tensor.ndim == 2 and tensor.shape[1] % NVFP4_BLOCKSIZE == 0
     out_f, in_f = tensor.shape
-    blocks, scale_fp8, global_scale, inv_eff = _scales(tensor.float(), eps)
+    blocks, scale_fp8, global_scale, inv_eff = _scales(tensor.float(), eps, amax)
     codes = _quantize_fp4_e2m1_rne(blocks * inv_eff.unsqueeze(-1)).reshape(out_f, in_f)
     return pack_fp4(codes), scale_fp8, global_scale
 
@@ -177,11 +178,16 @@ class NVFP4QWeight(QWeightBase):
         return dequantize_nvfp4_blockwise(self.weight_packed, self.block_scale_fp8, self.global_scale,
                                           self.in_f, dtype)
 
+    USES_TENSOR_AMAX = True
+
+    def _payload_rows(self, lo, hi):
+        return [self.weight_packed[lo:hi], self.block_scale_fp8[lo:hi], self.global_scale]
+
     def _quantize_into(self, src: Tensor, amax=None) -> None:
         if self.weight_packed.is_cuda and src.is_cuda and src.dtype in _CUDA_DTYPES and _supports_native_fp4():
             _quantize_nvfp4_cuda(src, self.weight_packed, self.block_scale_fp8, self.global_scale, amax=amax)
             return
-        packed, scale, gs = quantize_nvfp4_blockwise(src.to(self.weight_packed.device))
+        packed, scale, gs = quantize_nvfp4_blockwise(src.to(self.weight_packed.device), amax=amax)
         self.weight_packed.copy_(packed)
         self.block_scale_fp8.copy_(scale)
         self.global_scale.copy_(gs)

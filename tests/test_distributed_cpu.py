@@ -246,3 +246,67 @@ def test_missing_rank_surfaces_as_error_not_hang():
     with tempfile.TemporaryDirectory() as d:
         mp.spawn(_lonely_worker, args=(free_port(), d), nprocs=WORLD, join=True)
         assert torch.load(os.path.join(d, "rank0.pt")) != "no error"
+
+
+# ---------------------------------------------------- sharded QAT: quantize on the owner
+class QNet(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.l1 = nn.Linear(128, 256, bias=False)
+        self.l2 = nn.Linear(256, 128, bias=False)
+
+    def forward(self, x):
+        return self.l2(torch.relu(self.l1(x)))
+
+
+def _qat_worker(rank, port, fmt, out_dir):
+    from offload_adam_b200.qweight import Int4QWeight, Int8QWeight, NF4QWeight, NVFP4QWeight, quantize_linears
+    cls = {"nvfp4": NVFP4QWeight, "nf4": NF4QWeight, "int4": Int4QWeight, "int8": Int8QWeight}[fmt]
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        torch.manual_seed(0)
+        model = QNet().to(torch.bfloat16)
+        quantize_linears(model, cls)
+        opt = DistributedOffloadAdam(model, lr=1e-2, weight_decay=0.01, mode="fp32_master", max_grad_norm=1.0,
+                                     decoupled_weight_decay=True)
+        assert all(p in opt._sharded for p in model.parameters())
+        g = torch.Generator().manual_seed(7 + rank)
+        for _ in range(2):
+            opt.ready_for_optimizer_step = True
+            x = torch.randn(8, 128, generator=g).to(torch.bfloat16)
+            model(x).float().pow(2).mean().backward()
+            opt.step()
+        opt.synchronize()
+        report = {}
+        for name, p in model.named_parameters():
+            shard = opt.state[p]["master_params"]
+            parts = [torch.empty_like(shard) for _ in range(WORLD)]
+            dist.all_gather(parts, shard.contiguous())
+            full = torch.cat(parts, dim=0)
+            # what the gather-fp32-then-requantize-everything route gives
+            want = cls.from_float(full.to(torch.bfloat16))
+            want.copy_(full)
+            got = p.data
+            report[name] = [torch.equal(a.view(torch.uint8) if a.element_size() == 1 else a,
+                                        b.view(torch.uint8) if b.element_size() == 1 else b)
+                            for a, b in zip(got._payload(), want._payload())]
+            report[name + ".payload"] = [t.clone() for t in got._payload()]
+        torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "nf4", "int4", "int8"])
+def test_sharded_qat_owner_quantizes_and_gathers_packed_rows(fmt):
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_qat_worker, args=(free_port(), fmt, d), nprocs=WORLD, join=True)
+        reps = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(WORLD)]
+    for name in ("l1.weight", "l2.weight"):
+        for rep in reps:
+            assert all(rep[name]), (fmt, name, rep[name])
+        for a, b in zip(reps[0][name + ".payload"], reps[1][name + ".payload"]):
+            a = a.view(torch.uint8) if a.element_size() == 1 else a
+            b = b.view(torch.uint8) if b.element_size() == 1 else b
+            assert torch.equal(a, b), (fmt, name, "replicas differ")

@@ -149,3 +149,67 @@ def test_symm_path_matches_restatement_and_collectives():
             if key.endswith("/None"):
                 # without clipping there is no cross-rank scalar: bit-exact by construction
                 assert r["exact"], (key, r)
+
+
+# ------------------------------------------- sharded QAT: owners quantize, packed rows travel
+class QNet(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.l1 = nn.Linear(256, 512, bias=False)
+        self.l2 = nn.Linear(512, 256, bias=False)
+
+    def forward(self, x):
+        return self.l2(torch.relu(self.l1(x)))
+
+
+def _bits(t):
+    return t.view(torch.uint8) if t.element_size() == 1 else t
+
+
+def _qat_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    report = {}
+    try:
+        from offload_adam_b200 import DistributedOffloadAdam
+        from offload_adam_b200.qweight import (Int4QWeight, Int8QWeight, NF4QWeight, NVFP4QWeight,
+                                               quantize_linears)
+        for name, cls in (("nvfp4", NVFP4QWeight), ("nf4", NF4QWeight), ("int4", Int4QWeight),
+                          ("int8", Int8QWeight)):
+            torch.manual_seed(0)
+            model = QNet().to(torch.bfloat16).to(device)
+            quantize_linears(model, cls)
+            opt = DistributedOffloadAdam(model, lr=1e-2, weight_decay=0.01, mode="fp32_master",
+                                         max_grad_norm=1.0, decoupled_weight_decay=True, comm="nccl")
+            g = torch.Generator().manual_seed(7 + rank)
+            for _ in range(2):
+                opt.ready_for_optimizer_step = True
+                x = torch.randn(8, 256, generator=g).to(torch.bfloat16).to(device)
+                model(x).float().pow(2).mean().backward()
+                opt.step()
+            opt.synchronize()
+            ok = True
+            for p in model.parameters():
+                shard = opt.state[p]["master_params"].to(device)
+                full = torch.empty(p.shape, dtype=torch.float32, device=device)
+                dist.all_gather_into_tensor(full.view(-1), shard.view(-1))
+                want = cls.from_float(torch.zeros(p.shape, dtype=torch.bfloat16, device=device))
+                want.copy_(full)  # the gather-fp32-and-requantize-everything route
+                ok = ok and all(torch.equal(_bits(a), _bits(b))
+                                for a, b in zip(p.data._payload(), want._payload()))
+            report[name] = ok
+    finally:
+        torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
+        dist.destroy_process_group()
+
+
+def test_sharded_qat_payload_matches_full_requantization():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_qat_worker, args=(2, free_port(), d), nprocs=2, join=True)
+        reports = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(2)]
+    for rep in reports:
+        assert rep == {"nvfp4": True, "nf4": True, "int4": True, "int8": True}, rep

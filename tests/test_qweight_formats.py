@@ -251,3 +251,35 @@ def test_gpu_linear_and_requantize(cls, kw):
     master = w.float() * 0.5
     q.data.copy_(master)
     assert torch.allclose(q.data.dequantize().float(), master, atol=0.15)
+
+
+# --------------------------------------------------------------- row shards
+def _same_bits(a, b):
+    a = a.view(torch.uint8) if a.element_size() == 1 else a
+    b = b.view(torch.uint8) if b.element_size() == 1 else b
+    return torch.equal(a, b)
+
+
+@pytest.mark.parametrize("device", ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)])
+@pytest.mark.parametrize("fmt", ["nvfp4", "nf4", "int4", "int8"])
+def test_row_shards_requantize_to_the_same_bits(fmt, device):
+    """Quantizing row ranges separately (as the owners of a sharded weight do) must
+    reproduce the whole-tensor quantization bit for bit."""
+    from offload_adam_b200.qweight import Int4QWeight, Int8QWeight, NF4QWeight, NVFP4QWeight
+    cls = {"nvfp4": NVFP4QWeight, "nf4": NF4QWeight, "int4": Int4QWeight, "int8": Int8QWeight}[fmt]
+    torch.manual_seed(1)
+    master = (torch.randn(256, 384, device=device) * 0.05)
+    master[200, 7] = 1.5  # the tensor-wide maximum sits in the last shard
+    whole = cls.from_float(torch.zeros(256, 384, dtype=torch.bfloat16, device=device))
+    whole.copy_(master)
+    split = cls.from_float(torch.zeros(256, 384, dtype=torch.bfloat16, device=device))
+    amax = master.abs().amax().reshape(1).float() if cls.USES_TENSOR_AMAX else None
+    for lo, hi in ((0, 64), (64, 128), (128, 256)):
+        shard, views = split.row_shard(lo, hi)
+        assert tuple(shard.shape) == (hi - lo, 384)
+        shard._quantize_into(master[lo:hi].contiguous(), amax)
+        for view, part in zip(views, shard._payload()):
+            if part.data_ptr() != view.data_ptr():
+                view.copy_(part)
+    for a, b in zip(whole._payload(), split._payload()):
+        assert _same_bits(a, b)
