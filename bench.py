@@ -67,8 +67,13 @@ def parse_args():
     ap.add_argument("--comm", default="auto", help="distributed path: auto | symm | nccl")
     ap.add_argument("--max-ctas", type=int, default=0)
     ap.add_argument("--staging-gib", type=float, default=None, help="size of the staging ring (default: optimizer default)")
+    ap.add_argument("--prefetch-inflight", type=int, default=None,
+                    help="early-H2D chunks in the copy engine at once (0: unbounded)")
     ap.add_argument("--grad-ckpt", action="store_true", help="activation checkpointing per layer")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--profile-range", action="store_true",
+                    help="after the timed region, run one more step between cudaProfilerStart/Stop "
+                         "(for `ncu --profile-from-start off`); not part of any reported number")
     ap.add_argument("--verbose", type=int, default=0)
     return ap.parse_args()
 
@@ -176,6 +181,8 @@ def build_ours(args, preset, device):
                   max_ctas=args.max_ctas, seed=1234)
     if args.staging_gib is not None:
         common["staging_bytes"] = int(args.staging_gib * 2**30)
+    if args.prefetch_inflight is not None:
+        common["prefetch_inflight"] = args.prefetch_inflight
     if preset["optimizer"] == "distributed":
         opt = DistributedOffloadAdam(model, comm=args.comm, **common)
     else:
@@ -332,6 +339,15 @@ def main():
     ms = max_over_ranks(ms, device)
     exposed_ms = max_over_ranks(exposed_ms, device)
     peak_gb = torch.cuda.max_memory_allocated() / 1024**3
+
+    if args.verbose > 2 and args.impl == "ours" and rank == 0:
+        print("[rank 0] last timed step, ms from its start:", opt.trace_report(), flush=True)
+    if args.profile_range:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        run_steps(1, ga, opt, loss_fn, batches_dev=dev_batches)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
 
     e2e = None
     if not args.skip_e2e:

@@ -52,6 +52,8 @@ class TransferEngine:
         self._inflight_bytes = 0
         self.h2d_stream = self.d2h_stream = self.opt_stream = None
         self._native = None
+        self.chunk_elems = int(chunk_elems)
+        self._marks, self._last_marks = [], []
         self.scratch = None
         self.staging_bytes = 0
         if self.cuda:
@@ -66,7 +68,10 @@ class TransferEngine:
                     # the early-H2D / trailing-D2H area
                     chunk_elems = max(16, int(chunk_elems) // 16 * 16)
                     floor = self.C.OffloadEngine.min_ring_bytes(chunk_elems)
-                    nbytes = max(floor, int(ring_slots) * chunk_elems * 10, int(staging_bytes))
+                    # the floor on top of the request: with all of a small shard's state
+                    # prefetched, the chunks loaded during the step still find room
+                    nbytes = max(int(ring_slots) * chunk_elems * 10, int(staging_bytes)) + floor
+                    self.chunk_elems = chunk_elems
                     nbytes = (nbytes + 255) // 256 * 256
                     ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
                     self.staging_bytes = nbytes
@@ -98,6 +103,33 @@ class TransferEngine:
                 self._native.join_compute(main.cuda_stream)
         else:
             main.wait_stream(self.opt_stream)
+
+    # ----------------------------------------------------------------- tracing
+    def mark(self, name, which="main"):
+        """Record a named timing event on one of the engine's streams (``'main'`` |
+        ``'opt'`` | ``'h2d'`` | ``'d2h'``).  Marks cost one event record each and are only
+        taken when the optimizer runs with ``verbose`` > 2; ``trace_report`` turns them
+        into milliseconds relative to the first mark of the step."""
+        if not self.cuda:
+            return
+        stream = {"main": torch.cuda.current_stream(self.device), "opt": self.opt_stream,
+                  "h2d": self.h2d_stream, "d2h": self.d2h_stream}[which]
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(stream)
+        self._marks.append((name, which, ev))
+
+    def begin_trace(self):
+        """Start a new trace; the previous one stays readable until then."""
+        self._last_marks, self._marks = self._marks, []
+
+    def trace_report(self, current=True):
+        """``{name@stream: ms since the first mark}`` of the current (or previous) trace;
+        ``None`` while some of its events have not completed.  Never blocks."""
+        marks = self._marks if current else self._last_marks
+        if not marks or not all(ev.query() for _, _, ev in marks):
+            return None
+        t0 = marks[0][2]
+        return {f"{name}@{which}": round(t0.elapsed_time(ev), 3) for name, which, ev in marks}
 
     @property
     def can_prefetch(self):

@@ -92,6 +92,11 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         grad_residency: ``'auto'`` | ``'host'`` | ``'device'``.
         device_grad_budget: bytes of HBM ``'auto'`` may spend on gradient
             accumulators (default: a quarter of the device's memory).
+        prefetch_inflight: early-H2D chunks allowed in the copy engine at once (default 1:
+            a copy the caller issues, such as an input batch, waits behind one chunk at
+            most); 0 queues everything that fits in the staging buffer as soon as a step
+            ends, which keeps the link busy through the step but makes other H2D copies
+            wait behind it.
         chunk_elems: elements per staged chunk (default 8 Mi divided by the world size,
             at least 1 Mi).
         staging_bytes: HBM set aside for the circular staging buffer of the staged transfer
@@ -129,7 +134,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                  decoupled_weight_decay=False, inplace_param_threshold=None,
                  prefetch_policy="eager", verbose=0, *, transfer="auto", grad_residency="auto",
                  device_grad_budget=None, chunk_elems=None, ring_slots=4, max_ctas=0,
-                 max_inflight_bytes=8 << 30, staging_bytes=8 << 30, seed=None):
+                 max_inflight_bytes=8 << 30, staging_bytes=8 << 30, prefetch_inflight=1, seed=None):
         if prefetch_policy not in ("eager", "lazy"):
             raise ValueError(f"prefetch_policy must be 'eager' or 'lazy' (got {prefetch_policy!r})")
         if grad_residency not in ("auto", "host", "device"):
@@ -213,9 +218,10 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                 grad_residency = "host"
         self.grad_residency = grad_residency
         if chunk_elems is None:
-            # a slot holds one chunk of one tensor: keep chunks near the size of a typical
-            # (sharded) tensor so that small tensors do not waste ring space
+            # smaller shards, smaller chunks: the pipeline of a step still has several
+            # chunks per tensor to overlap
             chunk_elems = max(1 << 20, (8 << 20) // max(1, getattr(self, "_world_size", 1)))
+        self.prefetch_inflight = int(prefetch_inflight)
         self._engine = TransferEngine(
             self.device, mode, len(params), transfer=transfer, chunk_elems=chunk_elems,
             ring_slots=ring_slots, max_ctas=max_ctas, max_inflight_bytes=max_inflight_bytes,
@@ -558,23 +564,31 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         if order is None:
             return
         eng = self._engine
-        if self._pf_idx >= len(order):
-            self._pf_order = None
-            return
-        p = order[self._pf_idx]
-        if p in self._quant_params:
-            self._pf_order = None  # takes its own route through a device temporary
-            return
-        st = self.state[p]
-        states = {k: st[k] for k in self._non_grad_keys}
-        off, full = eng.prefetch(self._pid[p], states, None, self._pf_off, max_chunks, max_inflight=1)
-        if full:
-            self._pf_order = None  # no staging space left for this step
-        elif off >= states["exp_avg"].numel():
-            self._pf_idx += 1
-            self._pf_off = 0
-        else:
-            self._pf_off = off  # an earlier copy is still in flight, or the budget is used up
+        inflight = self.prefetch_inflight
+        budget = max_chunks if inflight > 0 else 1 << 30  # unbounded: everything that fits, at once
+        while budget > 0:
+            if self._pf_idx >= len(order):
+                self._pf_order = None
+                return
+            p = order[self._pf_idx]
+            if p in self._quant_params:
+                self._pf_order = None  # takes its own route through a device temporary
+                return
+            st = self.state[p]
+            states = {k: st[k] for k in self._non_grad_keys}
+            off, full = eng.prefetch(self._pid[p], states, None, self._pf_off, budget, max_inflight=inflight)
+            if full:
+                self._pf_order = None  # no staging space left for this step
+                return
+            issued = -(-(off - self._pf_off) // eng.chunk_elems)
+            if off >= states["exp_avg"].numel():
+                self._pf_idx += 1
+                self._pf_off = 0
+            else:
+                self._pf_off = off
+            if issued == 0:
+                return  # earlier copies are still in flight
+            budget -= issued
 
     def _finish_step(self):
         """Run what the hooks deferred and make the main stream wait for the side
@@ -607,7 +621,16 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             print(f"{self._log_prefix()}step: {nat.prefetched_chunks()} chunk(s), "
                   f"{nat.prefetched_bytes() / 2**30:.2f} of {nat.ring_bytes() / 2**30:.2f} GiB of staging "
                   f"hold prefetched state", flush=True)
+        trace = self.verbose > 2
+        eng = self._engine
+        if trace:
+            eng.begin_trace()
+            eng.mark("step_begin")
+            eng.mark("earlier_loads_done", "h2d")
+            eng.mark("earlier_writebacks_done", "d2h")
         clip = self._global_clip_coef()
+        if trace:
+            eng.mark("clip_coef_done")
         inplace = []
         for group in self.param_groups:
             for p in group["params"]:
@@ -617,7 +640,13 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                 else:
                     self._step_offload(p, group, clip_coef=clip)
         self._step_inplace_batch(inplace, clip_coef=clip)
+        if trace:
+            eng.mark("kernels_done", "opt")
+            eng.mark("loads_done", "h2d")
+            eng.mark("writebacks_done", "d2h")
         self._finish_step()
+        if trace:
+            eng.mark("step_end")
         if self.max_grad_norm is not None:
             torch.sqrt(self._normsq, out=self._norms)
             self._normsq.zero_()
@@ -626,9 +655,10 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         """Device scalar min(1, max_norm / (||g|| + 1e-6)); no host sync."""
         if self.max_grad_norm is None:
             return None
-        # squared norms were written on the side stream (host residency) or on the
-        # main stream (device residency); order the reduction after both
-        self._engine.join_main()
+        # squared norms were written by kernels on the optimizer stream (host residency)
+        # or on the main stream (device residency); order the reduction after both.
+        # Copies still in flight (early loads, trailing write-backs) are not waited for.
+        self._engine.join_main(wait_writeback=False)
         grad_ops.clip_finalize(self._normsq, None, None, self.max_grad_norm, coef_norm=self._clip)
         return self._clip[0:1]
 
@@ -640,6 +670,13 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         """Same layout as the reference; waits for write-backs still in flight first."""
         self.synchronize()
         return super().state_dict()
+
+    def trace_report(self, current=True):
+        """Timeline of the last one-shot ``step()`` taken with ``verbose`` > 2 (see
+        ``TransferEngine.mark``): milliseconds from the start of the step to named points
+        on the main, optimizer, H2D and D2H streams.  ``None`` until the step's work has
+        completed; never blocks."""
+        return self._engine.trace_report(current)
 
     def synchronize(self):
         """Block the host until every enqueued transfer and step has finished."""

@@ -323,7 +323,7 @@ class DistributedOffloadAdam(OffloadAdam):
             return self._symm.global_clip_coef()
         # sharded params contribute disjoint slices on every rank; replicated ones are
         # identical everywhere and are counted by rank 0 only
-        self._engine.join_main()
+        self._engine.join_main(wait_writeback=False)
         idx = [self._pid[p] for p in self._all_params if p in self._sharded or self._rank == 0]
         index = torch.tensor(idx, dtype=torch.int32, device=self.device)
         local = torch.zeros(1, dtype=torch.float32, device=self.device)

@@ -244,7 +244,7 @@ class SymmZero1:
     def global_clip_coef(self):
         opt, C = self.opt, self.C
         self.reduce_small_bucket()
-        opt._engine.join_main()  # slice norms were produced on the optimizer stream
+        opt._engine.join_main(wait_writeback=False)  # slice norms come from kernels on the optimizer stream
         extra = self.small_sq if (self.rank == 0 and self.small) else None
         grad_ops.clip_finalize(opt._normsq if self.norm_index is not None else None, self.norm_index,
                                extra, opt.max_grad_norm, total_sq=self.local_sq)
