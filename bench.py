@@ -69,6 +69,8 @@ def parse_args():
     ap.add_argument("--staging-gib", type=float, default=None, help="size of the staging ring (default: optimizer default)")
     ap.add_argument("--prefetch-inflight", type=int, default=None,
                     help="early-H2D chunks in the copy engine at once (0: unbounded)")
+    ap.add_argument("--chunk-elems", type=int, default=None)
+    ap.add_argument("--sync-writeback", action="store_true", help="issue D2H write-backs inline")
     ap.add_argument("--grad-ckpt", action="store_true", help="activation checkpointing per layer")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--profile-range", action="store_true",
@@ -181,6 +183,10 @@ def build_ours(args, preset, device):
                   max_ctas=args.max_ctas, seed=1234)
     if args.staging_gib is not None:
         common["staging_bytes"] = int(args.staging_gib * 2**30)
+    if args.chunk_elems is not None:
+        common["chunk_elems"] = args.chunk_elems
+    if args.sync_writeback:
+        common["async_writeback"] = False
     if args.prefetch_inflight is not None:
         common["prefetch_inflight"] = args.prefetch_inflight
     if preset["optimizer"] == "distributed":

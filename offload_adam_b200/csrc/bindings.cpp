@@ -243,11 +243,12 @@ struct PyEngine {
   std::unique_ptr<oab::OffloadEngine> eng;
   Tensor workspace;  // keeps the slot ring alive
   PyEngine(int64_t device, int64_t compute, int64_t h2d, int64_t d2h, Tensor ws, int64_t chunk_elems,
-           int64_t max_ctas, int64_t n_tensors)
+           int64_t max_ctas, int64_t n_tensors, bool async_writeback)
       : workspace(std::move(ws)) {
     oab::EngineOptions o;
     o.chunk_elems = chunk_elems;
     o.max_ctas = (int)max_ctas;
+    o.async_writeback = async_writeback;
     TORCH_CHECK(workspace.is_cuda(), "engine workspace must be a CUDA tensor");
     eng = std::make_unique<oab::OffloadEngine>(
         (int)device, reinterpret_cast<cudaStream_t>(compute), reinterpret_cast<cudaStream_t>(h2d),
@@ -281,7 +282,11 @@ struct PyEngine {
     k.seed = (uint64_t)seed;
     k.elem_offset = elem_offset;
     if (amax.has_value() && amax->defined()) k.amax_out = amax->data_ptr<float>();
-    eng->staged_step(a);
+    {
+      // may wait for staging space (write-backs issued by the helper thread)
+      py::gil_scoped_release nogil;
+      eng->staged_step(a);
+    }
   }
   void staged_grad_to_host(int64_t pid, const Tensor& host_grad, const Tensor& dev_grad, bool first,
                            const OptT& sumsq, const OptT& scratch) {
@@ -306,7 +311,11 @@ struct PyEngine {
     int64_t off = eng->prefetch(a, from_off, max_chunks, (int)max_inflight, &full);
     return {off, full};
   }
-  void join(int64_t stream) { eng->join(pick_stream(stream)); }
+  void join(int64_t stream) {
+    cudaStream_t s = pick_stream(stream);
+    py::gil_scoped_release nogil;
+    eng->join(s);
+  }
   void join_compute(int64_t stream) { eng->join_compute(pick_stream(stream)); }
   void discard_prefetched() { eng->discard_prefetched(); }
   int64_t prefetched_chunks() const { return eng->prefetched_chunks(); }
@@ -360,7 +369,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("stats", &PyArena::stats);
 
   py::class_<PyEngine>(m, "OffloadEngine")
-      .def(py::init<int64_t, int64_t, int64_t, int64_t, Tensor, int64_t, int64_t, int64_t>())
+      .def(py::init<int64_t, int64_t, int64_t, int64_t, Tensor, int64_t, int64_t, int64_t, bool>())
       .def_static("min_ring_bytes", [](int64_t chunk_elems) {
         return (int64_t)oab::OffloadEngine::min_ring_bytes(chunk_elems);
       })

@@ -45,9 +45,21 @@ OffloadEngine::OffloadEngine(int device, cudaStream_t compute, cudaStream_t h2d,
   for (auto& e : grad_ready_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event");
   check(cudaEventCreateWithFlags(&tmp_ev_, cudaEventDisableTiming), "event");
   for (auto& e : join_ev_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event");
+  wb_submitted_.assign(n_tensors, 0);
+  wb_issued_.reset(new std::atomic<int64_t>[n_tensors > 0 ? n_tensors : 1]);
+  for (int i = 0; i < n_tensors; ++i) wb_issued_[i].store(0);
+  if (opt_.async_writeback) writer_ = std::thread([this] { writer_loop(); });
 }
 
 OffloadEngine::~OffloadEngine() {
+  if (writer_.joinable()) {
+    {
+      std::lock_guard<std::mutex> lk(wb_mu_);
+      wb_stop_ = true;
+    }
+    wb_cv_.notify_all();
+    writer_.join();
+  }
   for (auto& e : all_events_) cudaEventDestroy(e);
   for (auto& e : host_ready_) if (e) cudaEventDestroy(e);
   for (auto& e : grad_ready_) if (e) cudaEventDestroy(e);
@@ -67,9 +79,72 @@ cudaEvent_t OffloadEngine::take_event() {
   return e;
 }
 
+// ---------------------------------------------------------------- write-backs
+void OffloadEngine::issue_writeback(const WbJob& j, cudaError_t* err) {
+  cudaError_t e = cudaStreamWaitEvent(d2h_, j.k_done, 0);
+  for (int i = 0; i < j.n && e == cudaSuccess; ++i)
+    e = cudaMemcpyAsync(j.host[i], j.dev[i], j.bytes[i], cudaMemcpyDeviceToHost, d2h_);
+  if (e == cudaSuccess) e = cudaEventRecord(j.free_ev, d2h_);
+  if (e == cudaSuccess && j.pid >= 0) e = cudaEventRecord(host_ready_[j.pid], d2h_);
+  // retire even after an error: nobody may wait for this chunk forever
+  j.e->retired.store(true, std::memory_order_release);
+  if (j.pid >= 0) wb_issued_[j.pid].fetch_add(1, std::memory_order_release);
+  *err = e;
+}
+
+void OffloadEngine::submit_writeback(const WbJob& j) {
+  if (j.pid >= 0) {
+    ++wb_submitted_[j.pid];
+    host_ready_set_[j.pid] = 1;
+  }
+  if (!writer_.joinable()) {
+    cudaError_t e = cudaSuccess;
+    issue_writeback(j, &e);
+    check(e, "write-back");
+    return;
+  }
+  j.e->queued = true;
+  {
+    std::lock_guard<std::mutex> lk(wb_mu_);
+    if (!wb_error_.empty()) throw std::runtime_error("OffloadEngine: write-back failed: " + wb_error_);
+    wb_q_.push_back(j);
+  }
+  wb_cv_.notify_one();
+}
+
+void OffloadEngine::writer_loop() {
+  cudaSetDevice(device_);
+  for (;;) {
+    WbJob j;
+    {
+      std::unique_lock<std::mutex> lk(wb_mu_);
+      wb_cv_.wait(lk, [&] { return wb_stop_ || !wb_q_.empty(); });
+      if (wb_q_.empty()) return;  // stop requested and everything issued
+      j = wb_q_.front();
+      wb_q_.pop_front();
+      wb_busy_ = true;
+    }
+    cudaError_t e = cudaSuccess;
+    issue_writeback(j, &e);  // may block while the stream's queue is full: that is the point
+    {
+      std::lock_guard<std::mutex> lk(wb_mu_);
+      wb_busy_ = false;
+      if (e != cudaSuccess && wb_error_.empty()) wb_error_ = cudaGetErrorString(e);
+      if (wb_q_.empty()) wb_idle_cv_.notify_all();
+    }
+  }
+}
+
+void OffloadEngine::drain_writer() {
+  if (!writer_.joinable()) return;
+  std::unique_lock<std::mutex> lk(wb_mu_);
+  wb_idle_cv_.wait(lk, [&] { return wb_q_.empty() && !wb_busy_; });
+  if (!wb_error_.empty()) throw std::runtime_error("OffloadEngine: write-back failed: " + wb_error_);
+}
+
 void OffloadEngine::discard_prefetched() {
   // the chunks stay where they are until their space is needed; nothing reads them
-  for (Entry* e : loaded_) e->retired = true;
+  for (Entry* e : loaded_) e->retired.store(true, std::memory_order_release);
   loaded_.clear();
   inflight_.clear();
   loaded_bytes_ = 0;
@@ -92,7 +167,11 @@ OffloadEngine::Entry* OffloadEngine::allocate(size_t bytes, bool may_discard) {
     bool blocked = false;
     for (const Entry& e : live_) {
       if (!overlaps(e)) break;
-      if (!e.retired) { blocked = true; break; }
+      if (e.queued) {
+        // its write-back is with the helper thread: it will be issued, wait for that
+        while (!e.retired.load(std::memory_order_acquire)) std::this_thread::yield();
+      }
+      if (!e.retired.load(std::memory_order_acquire)) { blocked = true; break; }
     }
     if (blocked) {
       if (may_discard && !loaded_.empty()) { discard_prefetched(); continue; }
@@ -123,8 +202,12 @@ OffloadEngine::Entry* OffloadEngine::allocate(size_t bytes, bool may_discard) {
 
 void OffloadEngine::wait_host_copy(const StagedStepArgs& a) {
   // the host copy must be complete: the previous write-back of this tensor
-  if (a.pid >= 0 && a.pid < (int)host_ready_.size() && host_ready_set_[a.pid])
+  if (a.pid >= 0 && a.pid < (int)host_ready_.size() && host_ready_set_[a.pid]) {
+    // the event must have been recorded by the helper thread before it can be waited for
+    while (wb_issued_[a.pid].load(std::memory_order_acquire) < wb_submitted_[a.pid])
+      std::this_thread::yield();
     check(cudaStreamWaitEvent(h2d_, host_ready_[a.pid], 0), "wait host_ready");
+  }
   if (a.host_grad && a.pid >= 0 && a.pid < (int)grad_ready_.size() && grad_ready_set_[a.pid])
     check(cudaStreamWaitEvent(h2d_, grad_ready_[a.pid], 0), "wait grad_ready");
 }
@@ -230,21 +313,23 @@ void OffloadEngine::staged_step(const StagedStepArgs& a) {
     for (int j = 0; j < k.n_p_peers; ++j) c.p_peers[j] = (char*)k.p_peers[j] + 2 * off;
     check(launch_adam_step(c, compute_), "adam_step");
     check(cudaEventRecord(e->k_done, compute_), "record");
-    check(cudaStreamWaitEvent(d2h_, e->k_done, 0), "wait k");
 
-    check(cudaMemcpyAsync((char*)k.m + 2 * off, e->m, 2 * len, cudaMemcpyDeviceToHost, d2h_), "d2h m");
-    check(cudaMemcpyAsync((char*)k.v + 2 * off, e->v, 2 * len, cudaMemcpyDeviceToHost, d2h_), "d2h v");
+    WbJob j;
+    j.e = e;
+    j.k_done = e->k_done;
+    j.free_ev = e->free_ev;
+    j.host[0] = (char*)k.m + 2 * off; j.dev[0] = e->m; j.bytes[0] = 2 * len;
+    j.host[1] = (char*)k.v + 2 * off; j.dev[1] = e->v; j.bytes[1] = 2 * len;
+    j.n = 2;
     bytes_d2h_ += 4 * len;
     if (xb) {
-      check(cudaMemcpyAsync((char*)k.extra + xb * off, e->x, xb * len, cudaMemcpyDeviceToHost, d2h_), "d2h x");
+      j.host[2] = (char*)k.extra + xb * off; j.dev[2] = e->x; j.bytes[2] = xb * len;
+      j.n = 3;
       bytes_d2h_ += xb * len;
     }
-    check(cudaEventRecord(e->free_ev, d2h_), "record");
-    e->retired = true;
-  }
-  if (a.pid >= 0 && a.pid < (int)host_ready_.size()) {
-    check(cudaEventRecord(host_ready_[a.pid], d2h_), "record host_ready");
-    host_ready_set_[a.pid] = 1;
+    const bool last = off + C >= k.n;
+    j.pid = (last && a.pid >= 0 && a.pid < (int)host_ready_.size()) ? a.pid : -1;
+    submit_writeback(j);
   }
 }
 
@@ -293,7 +378,7 @@ void OffloadEngine::staged_grad_to_host(int pid, void* host_grad, const void* de
     check(cudaMemcpyAsync((char*)host_grad + 2 * off, sg, 2 * len, cudaMemcpyDeviceToHost, d2h_), "d2h g");
     bytes_d2h_ += 2 * len;
     check(cudaEventRecord(e->free_ev, d2h_), "record");
-    e->retired = true;
+    e->retired.store(true, std::memory_order_release);
     first_chunk = false;
   }
   if (tracked) {
@@ -303,6 +388,7 @@ void OffloadEngine::staged_grad_to_host(int pid, void* host_grad, const void* de
 }
 
 void OffloadEngine::join(cudaStream_t stream) {
+  drain_writer();
   cudaStream_t src[3] = {compute_, h2d_, d2h_};
   for (int i = 0; i < 3; ++i) {
     check(cudaEventRecord(join_ev_[i], src[i]), "record join");
@@ -316,6 +402,7 @@ void OffloadEngine::join_compute(cudaStream_t stream) {
 }
 
 void OffloadEngine::synchronize() {
+  drain_writer();
   check(cudaStreamSynchronize(compute_), "sync compute");
   check(cudaStreamSynchronize(h2d_), "sync h2d");
   check(cudaStreamSynchronize(d2h_), "sync d2h");

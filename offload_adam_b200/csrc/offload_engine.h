@@ -22,8 +22,14 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <condition_variable>
 #include <deque>
 #include <list>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
 #include <vector>
 
 #include "adam_step.h"
@@ -33,6 +39,14 @@ namespace oab {
 struct EngineOptions {
   int64_t chunk_elems = int64_t(8) << 20;  // largest chunk, in elements
   int max_ctas = 0;                        // grid cap for kernels on the compute stream
+  // Issue the D2H write-backs of a step from a helper thread.  A stream accepts only
+  // a bounded number of pending operations (about a thousand); beyond that the
+  // enqueueing call blocks.  A step of many chunks puts five operations per chunk on
+  // the D2H stream, so with inline issue the caller stalls as soon as the kernels are
+  // a couple of hundred chunks ahead of the write-backs, the remaining kernels are
+  // launched at the pace of the D2H link and whatever the caller wanted to launch next
+  // (the next forward pass) waits too.  With the helper thread only that thread blocks.
+  bool async_writeback = true;
 };
 
 struct StagedStepArgs {
@@ -99,14 +113,29 @@ class OffloadEngine {
   struct Entry {
     size_t off = 0, bytes = 0;  // placement in the buffer
     cudaEvent_t h2d_done = nullptr, k_done = nullptr, free_ev = nullptr;
-    bool retired = false;  // its D2H has been issued (or it was discarded): the memory may
-                           // be reused once free_ev has fired
+    std::atomic<bool> retired{false};  // its D2H has been issued (or it was discarded): the
+                                       // memory may be reused once free_ev has fired
+    bool queued = false;   // handed to the write-back thread, which will retire it
     // content, for prefetched chunks
     int pid = -1;
     int64_t eoff = 0, len = 0;
     bool has_grad = false;
     char *g = nullptr, *m = nullptr, *v = nullptr, *x = nullptr;  // sub-buffers
   };
+  // One chunk's write-back, as handed to the helper thread (everything by value).
+  struct WbJob {
+    Entry* e = nullptr;
+    void* host[3] = {nullptr, nullptr, nullptr};
+    const void* dev[3] = {nullptr, nullptr, nullptr};
+    size_t bytes[3] = {0, 0, 0};
+    int n = 0;
+    cudaEvent_t k_done = nullptr, free_ev = nullptr;
+    int pid = -1;  // >= 0: last chunk of that tensor, record host_ready_[pid] after it
+  };
+  void issue_writeback(const WbJob& j, cudaError_t* err);
+  void submit_writeback(const WbJob& j);
+  void writer_loop();
+  void drain_writer();
   Entry* allocate(size_t bytes, bool may_discard);
   Entry* load_chunk(const StagedStepArgs& a, int64_t off, int64_t len, bool may_discard);
   cudaEvent_t take_event();
@@ -131,6 +160,15 @@ class OffloadEngine {
   cudaEvent_t tmp_ev_ = nullptr;
   cudaEvent_t join_ev_[3] = {nullptr, nullptr, nullptr};
   int64_t bytes_h2d_ = 0, bytes_d2h_ = 0;
+  // write-back thread
+  std::thread writer_;
+  std::mutex wb_mu_;
+  std::condition_variable wb_cv_, wb_idle_cv_;
+  std::deque<WbJob> wb_q_;
+  bool wb_stop_ = false, wb_busy_ = false;
+  std::string wb_error_;
+  std::vector<int64_t> wb_submitted_;                  // per tensor, by the caller
+  std::unique_ptr<std::atomic<int64_t>[]> wb_issued_;  // per tensor, by the helper thread
 };
 
 }  // namespace oab

@@ -92,20 +92,22 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         grad_residency: ``'auto'`` | ``'host'`` | ``'device'``.
         device_grad_budget: bytes of HBM ``'auto'`` may spend on gradient
             accumulators (default: a quarter of the device's memory).
-        prefetch_inflight: early-H2D chunks allowed in the copy engine at once (default 1:
-            a copy the caller issues, such as an input batch, waits behind one chunk at
-            most); 0 queues everything that fits in the staging buffer as soon as a step
+        prefetch_inflight: early-H2D chunks allowed in the copy engine at once (default 2:
+            a copy the caller issues, such as an input batch, waits behind two chunks at
+            most, a few milliseconds); 0 queues everything that fits in the staging buffer as soon as a step
             ends, which keeps the link busy through the step but makes other H2D copies
             wait behind it.
-        chunk_elems: elements per staged chunk (default 8 Mi divided by the world size,
-            at least 1 Mi).
-        staging_bytes: HBM set aside for the circular staging buffer of the staged transfer
-            (default 8 GiB, capped at this rank's state size; about what the reference
-            keeps on the GPU as whole state tensors in flight: two of the 4.2 GB
-            embedding-sized states of an 8B model).  State of the first tensors of the next step is brought
-            into it ahead of time and the last write-backs of a step drain from it while
-            the next forward runs, so up to this many bytes per direction leave the
-            exposed part of the step.
+        async_writeback: issue the D2H write-backs of the staged transfer from a helper
+            thread, so that the caller never blocks on a full stream queue (default).
+        chunk_elems: elements per staged chunk (default 8 Mi).
+        staging_bytes: HBM set aside for the circular staging buffer of the staged
+            transfer.  State of the first tensors of the next step is brought into it
+            while forward/backward run and the last write-backs of a step drain from it
+            while the next forward runs, so the host link works through the whole
+            iteration instead of only during the exposed part of the step.  ``None``
+            (default): this rank's state size, at most a quarter of the device's memory
+            (the same budget rule as ``device_grad_budget``).  A few hundred MB are
+            enough for the step itself; everything above that buys overlap.
         max_ctas: grid cap of the streaming kernels (0: kernel default); small
             values leave the SMs to the concurrent backward GEMMs.
         seed: seeds the stochastic-rounding stream.
@@ -134,7 +136,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                  decoupled_weight_decay=False, inplace_param_threshold=None,
                  prefetch_policy="eager", verbose=0, *, transfer="auto", grad_residency="auto",
                  device_grad_budget=None, chunk_elems=None, ring_slots=4, max_ctas=0,
-                 max_inflight_bytes=8 << 30, staging_bytes=8 << 30, prefetch_inflight=1, seed=None):
+                 max_inflight_bytes=8 << 30, staging_bytes=None, prefetch_inflight=2, async_writeback=True, seed=None):
         if prefetch_policy not in ("eager", "lazy"):
             raise ValueError(f"prefetch_policy must be 'eager' or 'lazy' (got {prefetch_policy!r})")
         if grad_residency not in ("auto", "host", "device"):
@@ -218,14 +220,15 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                 grad_residency = "host"
         self.grad_residency = grad_residency
         if chunk_elems is None:
-            # smaller shards, smaller chunks: the pipeline of a step still has several
-            # chunks per tensor to overlap
-            chunk_elems = max(1 << 20, (8 << 20) // max(1, getattr(self, "_world_size", 1)))
+            # large chunks: every chunk costs five operations on the D2H stream and a
+            # stream takes about a thousand pending operations before enqueueing blocks
+            chunk_elems = 8 << 20
         self.prefetch_inflight = int(prefetch_inflight)
         self._engine = TransferEngine(
             self.device, mode, len(params), transfer=transfer, chunk_elems=chunk_elems,
             ring_slots=ring_slots, max_ctas=max_ctas, max_inflight_bytes=max_inflight_bytes,
-            staging_bytes=min(int(staging_bytes), self._estimate_pinned_bytes(self._offload_params)),
+            staging_bytes=self._resolve_staging_bytes(staging_bytes),
+            async_writeback=async_writeback,
         )
         self.transfer = self._engine.transfer
         self.h2d_stream = self._engine.h2d_stream
@@ -381,6 +384,14 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         # hook only records the order in which owner modules are reached, which
         # diagnostics and the distributed subclass use.
         return None
+
+    def _resolve_staging_bytes(self, staging_bytes):
+        state = self._estimate_pinned_bytes(self._offload_params)
+        if staging_bytes is None:
+            staging_bytes = state
+            if self._cuda:
+                staging_bytes = min(state, torch.cuda.get_device_properties(self.device).total_memory // 4)
+        return min(int(staging_bytes), state)
 
     def _hp(self, group):
         b1, b2 = group["betas"]
