@@ -53,7 +53,7 @@ PRESETS = {
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--preset", choices=list(PRESETS), default="zero1")
@@ -239,7 +239,7 @@ def build_reference(args, preset, device):
 
 # ------------------------------------------------------------------------ training
 def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, device=None,
-              exposed=None, read_loss=lambda t: t.float().item()):
+              exposed=None, read_loss=lambda t: t.float().item(), host_times=None):
     """One entry of ``batches_*`` per micro-batch (cycled).  With ``batches_host``
     (end-to-end mode) the token ids of a step are copied from pinned host memory at the
     start of that step, on a side stream as a data loader would, and the step's loss is
@@ -249,6 +249,7 @@ def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, de
     copy_stream = torch.cuda.Stream(device) if batches_host is not None else None
     for _ in range(n_steps):
         staged = None
+        t_host = [time.perf_counter()]
         if batches_host is not None:
             staged = []
             copy_stream.wait_stream(torch.cuda.current_stream(device))
@@ -270,18 +271,28 @@ def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, de
             loss = loss_fn(ids)
             (loss / ga).backward()
             last = loss.detach()
+        t_host.append(time.perf_counter())  # forward/backward enqueued
         if exposed is not None:
             e0 = torch.cuda.Event(enable_timing=True); e0.record()
         opt.step()
+        t_host.append(time.perf_counter())  # step() returned
         if exposed is not None:
             e1 = torch.cuda.Event(enable_timing=True); e1.record()
             exposed.append((e0, e1))
         if batches_host is not None:
             last = read_loss(last)  # device -> host read of the step's result (4 bytes)
+        t_host.append(time.perf_counter())
+        if host_times is not None:
+            host_times.append([round((b - a) * 1e3, 1) for a, b in zip(t_host, t_host[1:])])
     return last
 
 
 def timed(fn, device):
+    """Returns (event ms on the launching stream, host wall ms until ``fn`` returned,
+    drain ms, fn's result).  Bracketed by barrier + synchronize on both sides.  The
+    drain is what was still running on other streams when the launching stream was
+    done: the write-back of the last step's optimizer state, which in a longer run
+    overlaps the next forward pass."""
     dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -289,10 +300,13 @@ def timed(fn, device):
     e0.record()
     out = fn()
     e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
     wall = time.perf_counter() - t0
-    return e0.elapsed_time(e1), wall * 1e3, out
+    e1.synchronize()
+    t1 = time.perf_counter()
+    torch.cuda.synchronize()
+    drain = time.perf_counter() - t1
+    dist.barrier()
+    return e0.elapsed_time(e1), wall * 1e3, drain * 1e3, out
 
 
 def main():
@@ -337,12 +351,13 @@ def main():
     if args.impl == "ours":
         launches0 = C.launch_count()
     exposed = []
-    ms, wall_ms, _ = timed(lambda: run_steps(args.steps, ga, opt, loss_fn, batches_dev=dev_batches,
-                                             exposed=exposed), device)
+    ms, wall_ms, drain_ms, _ = timed(lambda: run_steps(args.steps, ga, opt, loss_fn, batches_dev=dev_batches,
+                                                       exposed=exposed), device)
     launches = (C.launch_count() - launches0) if launches0 is not None else None
     clocks = sampler.stop()
     exposed_ms = statistics.mean(a.elapsed_time(b) for a, b in exposed) if exposed else None
     ms = max_over_ranks(ms, device)
+    drain_ms_all = max_over_ranks(drain_ms, device)
     exposed_ms = max_over_ranks(exposed_ms, device)
     peak_gb = torch.cuda.max_memory_allocated() / 1024**3
 
@@ -363,17 +378,22 @@ def main():
             from offload_adam_b200.utils.scalar import read_scalar as read_loss
         else:
             read_loss = lambda t: t.float().item()  # noqa: E731
-        ms2, wall2, last_loss = timed(lambda: run_steps(args.steps, ga, opt, loss_fn,
+        host_times = [] if args.verbose > 2 else None
+        ms2, wall2, drain2, last_loss = timed(lambda: run_steps(args.steps, ga, opt, loss_fn, host_times=host_times,
                                                         batches_host=host_batches, device=device,
                                                         read_loss=read_loss), device)
         ms2 = max_over_ranks(max(ms2, 0.0), device)
         wall2 = max_over_ranks(wall2, device)
-        # the loss read-back makes the host wait for the device, so wall time and
-        # event time agree; report the larger of the two
+        # the loss read-back makes the host wait for the device, so the wall time until
+        # the last loss is on the host and the event time agree; report the larger
         t = max(ms2, wall2)
+        if host_times and rank == 0:
+            print("[rank 0] e2e host ms per step [stage inputs + enqueue fwd/bwd, step(), read loss]:",
+                  host_times, flush=True)
         e2e = {"value": tokens_per_step * args.steps / (t / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": ga * mb * seq * 8, "d2h_bytes_per_step": 4,
-               "ms_per_step": t / args.steps, "loss": last_loss}
+               "ms_per_step": t / args.steps, "loss": last_loss,
+               "drain_ms_after_region": max_over_ranks(drain2, device)}
 
     if rank == 0:
         value = tokens_per_step * args.steps / (ms / 1e3)
@@ -398,7 +418,12 @@ def main():
                 "staging_gib": (getattr(getattr(opt, "_engine", None), "staging_bytes", 0) or 0) / 2**30,
             },
             "exposed_opt_ms": exposed_ms, "peak_gpu_gb": peak_gb, "build_s": t_build,
-            "wall_ms_per_step": wall_ms / args.steps, "clocks": clocks,
+            "wall_ms_per_step": wall_ms / args.steps,
+            "drain_ms_after_region": drain_ms_all,
+            "timing": "CUDA events on the launching stream, barrier + synchronize on both sides; the "
+                      "write-back of the last step's optimizer state (drain_ms_after_region) finishes "
+                      "after the region, as it does behind the next forward pass in a longer run",
+            "clocks": clocks,
             "e2e": e2e, "gpu_launches": launches,
         }
         print(json.dumps(out))

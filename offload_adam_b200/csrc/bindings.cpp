@@ -311,6 +311,31 @@ struct PyEngine {
     int64_t off = eng->prefetch(a, from_off, max_chunks, (int)max_inflight, &full);
     return {off, full};
   }
+  void start_prefetch(int64_t mode, const std::vector<std::tuple<int64_t, Tensor, Tensor, OptT>>& items,
+                      int64_t max_inflight) {
+    std::vector<oab::OffloadEngine::PrefetchItem> plan;
+    plan.reserve(items.size());
+    for (const auto& it : items) {
+      oab::OffloadEngine::PrefetchItem x;
+      x.pid = (int)std::get<0>(it);
+      x.mode = (int)mode;
+      const Tensor& m = std::get<1>(it);
+      const Tensor& v = std::get<2>(it);
+      const OptT& extra = std::get<3>(it);
+      TORCH_CHECK(!m.is_cuda() && !v.is_cuda() && m.is_contiguous() && v.is_contiguous(), "host state expected");
+      x.n = m.numel();
+      x.m = m.data_ptr();
+      x.v = v.data_ptr();
+      if (extra.has_value() && extra->defined()) x.extra = extra->data_ptr();
+      plan.push_back(x);
+    }
+    py::gil_scoped_release nogil;
+    eng->start_prefetch(std::move(plan), (int)max_inflight);
+  }
+  void stop_prefetch() {
+    py::gil_scoped_release nogil;
+    eng->stop_prefetch();
+  }
   void join(int64_t stream) {
     cudaStream_t s = pick_stream(stream);
     py::gil_scoped_release nogil;
@@ -384,6 +409,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("join", &PyEngine::join)
       .def("join_compute", &PyEngine::join_compute)
       .def("discard_prefetched", &PyEngine::discard_prefetched)
+      .def("start_prefetch", &PyEngine::start_prefetch)
+      .def("stop_prefetch", &PyEngine::stop_prefetch)
       .def("prefetched_chunks", &PyEngine::prefetched_chunks)
       .def("prefetched_bytes", &PyEngine::prefetched_bytes)
       .def("ring_bytes", &PyEngine::ring_bytes)

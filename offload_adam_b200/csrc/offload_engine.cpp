@@ -1,5 +1,6 @@
 #include "offload_engine.h"
 
+#include <chrono>
 #include <stdexcept>
 #include <string>
 
@@ -49,9 +50,19 @@ OffloadEngine::OffloadEngine(int device, cudaStream_t compute, cudaStream_t h2d,
   wb_issued_.reset(new std::atomic<int64_t>[n_tensors > 0 ? n_tensors : 1]);
   for (int i = 0; i < n_tensors; ++i) wb_issued_[i].store(0);
   if (opt_.async_writeback) writer_ = std::thread([this] { writer_loop(); });
+  loader_ = std::thread([this] { loader_loop(); });
 }
 
 OffloadEngine::~OffloadEngine() {
+  if (loader_.joinable()) {
+    pf_stop_.store(true);
+    {
+      std::lock_guard<std::mutex> lk(pf_mu_);
+      pf_exit_ = true;
+    }
+    pf_cv_.notify_all();
+    loader_.join();
+  }
   if (writer_.joinable()) {
     {
       std::lock_guard<std::mutex> lk(wb_mu_);
@@ -143,6 +154,11 @@ void OffloadEngine::drain_writer() {
 }
 
 void OffloadEngine::discard_prefetched() {
+  stop_prefetch();
+  discard_impl();
+}
+
+void OffloadEngine::discard_impl() {
   // the chunks stay where they are until their space is needed; nothing reads them
   for (Entry* e : loaded_) e->retired.store(true, std::memory_order_release);
   loaded_.clear();
@@ -174,7 +190,7 @@ OffloadEngine::Entry* OffloadEngine::allocate(size_t bytes, bool may_discard) {
       if (!e.retired.load(std::memory_order_acquire)) { blocked = true; break; }
     }
     if (blocked) {
-      if (may_discard && !loaded_.empty()) { discard_prefetched(); continue; }
+      if (may_discard && !loaded_.empty()) { discard_impl(); continue; }
       return nullptr;
     }
     while (!live_.empty() && overlaps(live_.front())) {
@@ -244,8 +260,90 @@ OffloadEngine::Entry* OffloadEngine::load_chunk(const StagedStepArgs& a, int64_t
   return e;
 }
 
+// ------------------------------------------------------------- prefetch thread
+void OffloadEngine::start_prefetch(std::vector<PrefetchItem> items, int max_inflight) {
+  stop_prefetch();
+  {
+    std::lock_guard<std::mutex> lk(pf_mu_);
+    pf_plan_ = std::move(items);
+    pf_inflight_ = max_inflight > 0 ? max_inflight : 1;
+    pf_has_plan_ = true;
+    pf_active_.store(true);
+  }
+  pf_cv_.notify_all();
+}
+
+void OffloadEngine::stop_prefetch() {
+  if (!pf_active_.load()) return;
+  pf_stop_.store(true);
+  std::string err;
+  {
+    std::unique_lock<std::mutex> lk(pf_mu_);
+    pf_has_plan_ = false;
+    pf_plan_.clear();
+    pf_idle_cv_.wait(lk, [&] { return !pf_running_; });
+    err.swap(pf_error_);
+  }
+  pf_stop_.store(false);
+  pf_active_.store(false);
+  if (!err.empty()) throw std::runtime_error("OffloadEngine: prefetch failed: " + err);
+}
+
+void OffloadEngine::loader_loop() {
+  cudaSetDevice(device_);
+  for (;;) {
+    std::vector<PrefetchItem> plan;
+    int inflight = 1;
+    {
+      std::unique_lock<std::mutex> lk(pf_mu_);
+      pf_cv_.wait(lk, [&] { return pf_exit_ || pf_has_plan_; });
+      if (pf_exit_) return;
+      plan.swap(pf_plan_);
+      pf_has_plan_ = false;
+      pf_running_ = true;
+      inflight = pf_inflight_;
+    }
+    std::string err;
+    try {
+      bool done = false;
+      for (size_t i = 0; i < plan.size() && !done; ++i) {
+        StagedStepArgs a;
+        a.pid = plan[i].pid;
+        a.k.mode = plan[i].mode;
+        a.k.n = plan[i].n;
+        a.k.m = plan[i].m;
+        a.k.v = plan[i].v;
+        a.k.extra = plan[i].extra;
+        int64_t off = 0;
+        while (off < a.k.n) {
+          if (pf_stop_.load()) { done = true; break; }
+          bool full = false;
+          const int64_t now = prefetch_impl(a, off, 0, inflight, &full);
+          if (full) { done = true; break; }
+          if (now == off) std::this_thread::sleep_for(std::chrono::microseconds(50));
+          off = now;
+        }
+      }
+    } catch (const std::exception& ex) {
+      err = ex.what();
+    }
+    {
+      std::lock_guard<std::mutex> lk(pf_mu_);
+      pf_running_ = false;
+      if (!err.empty()) pf_error_ = err;
+    }
+    pf_idle_cv_.notify_all();
+  }
+}
+
 int64_t OffloadEngine::prefetch(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks,
                                 int max_inflight, bool* full) {
+  stop_prefetch();
+  return prefetch_impl(a, from_off, max_chunks, max_inflight, full);
+}
+
+int64_t OffloadEngine::prefetch_impl(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks,
+                                     int max_inflight, bool* full) {
   const AdamStepArgs& k = a.k;
   const int64_t C = opt_.chunk_elems;
   int64_t off = from_off, issued = 0;
@@ -275,6 +373,7 @@ int64_t OffloadEngine::prefetch(const StagedStepArgs& a, int64_t from_off, int64
 }
 
 void OffloadEngine::staged_step(const StagedStepArgs& a) {
+  stop_prefetch();
   const AdamStepArgs& k = a.k;
   const int64_t C = opt_.chunk_elems;
   const size_t xb = elem_extra_bytes(k.mode);
@@ -289,7 +388,7 @@ void OffloadEngine::staged_step(const StagedStepArgs& a) {
         loaded_.pop_front();
         loaded_bytes_ -= e->bytes;
       } else {
-        discard_prefetched();  // out-of-order step: give the space back
+        discard_impl();  // out-of-order step: give the space back
       }
     }
     if (e == nullptr) {
@@ -402,6 +501,7 @@ void OffloadEngine::join_compute(cudaStream_t stream) {
 }
 
 void OffloadEngine::synchronize() {
+  stop_prefetch();
   drain_writer();
   check(cudaStreamSynchronize(compute_), "sync compute");
   check(cudaStreamSynchronize(h2d_), "sync h2d");

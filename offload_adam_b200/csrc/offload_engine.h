@@ -86,6 +86,21 @@ class OffloadEngine {
   // wasted, nothing else).
   int64_t prefetch(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks, int max_inflight,
                    bool* full);
+  // The same early H2D, driven by a helper thread instead of by calls from the
+  // training loop: the thread walks `items` in order and keeps `max_inflight` chunk
+  // copies outstanding (polling their events between short sleeps) until the staging
+  // buffer is full, the plan is done or stop_prefetch() is called.  Pacing then does
+  // not depend on where the host thread is relative to the GPU.  Between
+  // start_prefetch() and stop_prefetch() the helper thread owns the staging buffer;
+  // every entry point that touches the buffer stops it first.
+  struct PrefetchItem {
+    int pid = -1;
+    int mode = 0;
+    int64_t n = 0;
+    void *m = nullptr, *v = nullptr, *extra = nullptr;
+  };
+  void start_prefetch(std::vector<PrefetchItem> items, int max_inflight);
+  void stop_prefetch();
   int64_t prefetched_chunks() const { return (int64_t)loaded_.size(); }
   int64_t prefetched_bytes() const { return (int64_t)loaded_bytes_; }
   void discard_prefetched();
@@ -132,6 +147,10 @@ class OffloadEngine {
     cudaEvent_t k_done = nullptr, free_ev = nullptr;
     int pid = -1;  // >= 0: last chunk of that tensor, record host_ready_[pid] after it
   };
+  int64_t prefetch_impl(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks,
+                        int max_inflight, bool* full);
+  void discard_impl();
+  void loader_loop();
   void issue_writeback(const WbJob& j, cudaError_t* err);
   void submit_writeback(const WbJob& j);
   void writer_loop();
@@ -167,6 +186,15 @@ class OffloadEngine {
   std::deque<WbJob> wb_q_;
   bool wb_stop_ = false, wb_busy_ = false;
   std::string wb_error_;
+  // prefetch thread
+  std::thread loader_;
+  std::mutex pf_mu_;
+  std::condition_variable pf_cv_, pf_idle_cv_;
+  std::vector<PrefetchItem> pf_plan_;
+  int pf_inflight_ = 1;
+  bool pf_has_plan_ = false, pf_running_ = false, pf_exit_ = false;
+  std::atomic<bool> pf_stop_{false}, pf_active_{false};
+  std::string pf_error_;
   std::vector<int64_t> wb_submitted_;                  // per tensor, by the caller
   std::unique_ptr<std::atomic<int64_t>[]> wb_issued_;  // per tensor, by the helper thread
 };

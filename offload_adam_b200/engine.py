@@ -131,6 +131,20 @@ class TransferEngine:
         t0 = marks[0][2]
         return {f"{name}@{which}": round(t0.elapsed_time(ev), 3) for name, which, ev in marks}
 
+    def start_prefetch(self, items, max_inflight=2):
+        """Hand a plan of early loads to the engine's helper thread: ``items`` is a list
+        of ``(pid, states)`` in the order the tensors will be stepped.  The thread keeps
+        ``max_inflight`` chunk copies outstanding until the staging buffer is full."""
+        if self._native is None or not items:
+            return
+        plan = [(pid, st["exp_avg"], st["exp_avg_sq"], st.get("master_params", st.get("rounding_error")))
+                for pid, st in items]
+        self._native.start_prefetch(self.mode_id, plan, int(max_inflight))
+
+    def stop_prefetch(self):
+        if self._native is not None:
+            self._native.stop_prefetch()
+
     @property
     def can_prefetch(self):
         return self._native is not None

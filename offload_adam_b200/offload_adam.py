@@ -92,6 +92,10 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         grad_residency: ``'auto'`` | ``'host'`` | ``'device'``.
         device_grad_budget: bytes of HBM ``'auto'`` may spend on gradient
             accumulators (default: a quarter of the device's memory).
+        prefetch_pacing: who issues the early H2D.  ``'thread'`` (default): a helper
+            thread of the copy engine, which keeps ``prefetch_inflight`` copies outstanding
+            whatever the training loop is doing; ``'hooks'``: the training thread itself,
+            one chunk at every forward pre-hook of a leaf module and every gradient hook.
         prefetch_inflight: early-H2D chunks allowed in the copy engine at once (default 2:
             a copy the caller issues, such as an input batch, waits behind two chunks at
             most, a few milliseconds); 0 queues everything that fits in the staging buffer as soon as a step
@@ -136,7 +140,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                  decoupled_weight_decay=False, inplace_param_threshold=None,
                  prefetch_policy="eager", verbose=0, *, transfer="auto", grad_residency="auto",
                  device_grad_budget=None, chunk_elems=None, ring_slots=4, max_ctas=0,
-                 max_inflight_bytes=8 << 30, staging_bytes=None, prefetch_inflight=2, async_writeback=True, seed=None):
+                 max_inflight_bytes=8 << 30, staging_bytes=None, prefetch_inflight=2, prefetch_pacing="thread", async_writeback=True,
+                 seed=None):
         if prefetch_policy not in ("eager", "lazy"):
             raise ValueError(f"prefetch_policy must be 'eager' or 'lazy' (got {prefetch_policy!r})")
         if grad_residency not in ("auto", "host", "device"):
@@ -224,6 +229,9 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             # stream takes about a thousand pending operations before enqueueing blocks
             chunk_elems = 8 << 20
         self.prefetch_inflight = int(prefetch_inflight)
+        if prefetch_pacing not in ("thread", "hooks"):
+            raise ValueError(f"prefetch_pacing must be 'thread' or 'hooks', got {prefetch_pacing!r}")
+        self.prefetch_pacing = prefetch_pacing
         self._engine = TransferEngine(
             self.device, mode, len(params), transfer=transfer, chunk_elems=chunk_elems,
             ring_slots=ring_slots, max_ctas=max_ctas, max_inflight_bytes=max_inflight_bytes,
@@ -270,8 +278,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         # the next forward must see every update even if the caller skipped step()
         model.register_forward_pre_hook(lambda *_: self._on_forward())
         # pacing points for the early H2D during forward (plain forward hooks add no
-        # autograd nodes)
-        for m in modules:
+        # autograd nodes); not needed when the helper thread paces
+        for m in (modules if self.prefetch_pacing == "hooks" else ()):
             if any(p.requires_grad and p not in self._inplace_params for p in m.parameters()):
                 m.register_forward_pre_hook(lambda *_: self._pace_prefetch(1))
 
@@ -564,6 +572,15 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             order = self._hook_order_prev
         else:
             order = [p for g in self.param_groups for p in g["params"] if p not in self._inplace_params]
+        if self.prefetch_pacing == "thread" and self.prefetch_inflight > 0:
+            items = []
+            for p in order or ():
+                if p in self._quant_params:
+                    break  # takes its own route through a device temporary
+                st = self.state[p]
+                items.append((self._pid[p], {k: st[k] for k in self._non_grad_keys}))
+            eng.start_prefetch(items, self.prefetch_inflight)
+            return
         self._pf_order = order or None
 
     def _pace_prefetch(self, max_chunks):
@@ -627,6 +644,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         if self._step_in_backward:
             self._finish_step()
             return
+        self._engine.stop_prefetch()
         if self.verbose > 1 and self._engine.can_prefetch:
             nat = self._engine._native
             print(f"{self._log_prefix()}step: {nat.prefetched_chunks()} chunk(s), "

@@ -263,3 +263,58 @@ def test_gpu_tiny_llama_trains_all_modes():
             losses.append(loss.item())
         opt.synchronize()
         assert losses[-1] < losses[0], (mode, losses)
+
+
+class Wide(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.layers = torch.nn.ModuleList([torch.nn.Linear(256, 256, bias=False) for _ in range(6)])
+
+    def forward(self, x):
+        for layer in self.layers:
+            x = torch.relu(layer(x))
+        return x
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("pacing", ["thread", "hooks"])
+@pytest.mark.parametrize("clip", [None, 0.05])
+@pytest.mark.parametrize("staging_chunks", [4, 1000])
+def test_gpu_early_loads_and_trailing_writebacks_are_exact(pacing, clip, staging_chunks):
+    """State loaded ahead of the step by the helper thread (or from hooks), write-backs
+    issued by the other helper thread, a staging buffer that is far too small (wraps,
+    refuses chunks, evicts) or large: parameters and state must equal the zero-copy path
+    bit for bit after several steps."""
+    ga, steps, chunk = 2, 6, 4096
+    g = torch.Generator().manual_seed(3)
+    data = [torch.randn(16, 256, generator=g).to(torch.bfloat16).cuda() for _ in range(ga * steps)]
+    kw = dict(lr=1e-2, weight_decay=0.05, mode="fp32_master", decoupled_weight_decay=True,
+              max_grad_norm=clip, inplace_param_threshold=100, grad_residency="device")
+
+    def net():
+        torch.manual_seed(0)
+        return Wide().to(torch.bfloat16).cuda()
+
+    m_a, m_b = net(), net()
+    o_a = OffloadAdam(m_a, transfer="staged", chunk_elems=chunk, ring_slots=3, prefetch_pacing=pacing,
+                      staging_bytes=staging_chunks * chunk * 8, **kw)
+    o_b = OffloadAdam(m_b, transfer="zero_copy", **kw)
+    seen = []
+    it = iter(data)
+    for _ in range(steps):
+        for micro in range(ga):
+            o_a.ready_for_optimizer_step = micro == ga - 1
+            (m_a(next(it)).float().pow(2).mean() / ga).backward()
+        if clip is not None:
+            o_a._engine.stop_prefetch()
+            seen.append(o_a._engine._native.prefetched_chunks())
+        o_a.step()
+    train(m_b, o_b, data, ga, steps)
+    o_a.synchronize()
+    if clip is not None:
+        assert max(seen[1:]) > 0, seen  # something was loaded ahead of a step
+    for a, b in zip(m_a.parameters(), m_b.parameters()):
+        assert torch.equal(a, b)
+    for p, q in zip(m_a.parameters(), m_b.parameters()):
+        for k in ("exp_avg", "exp_avg_sq", "master_params"):
+            assert torch.equal(o_a.state[p][k].cpu(), o_b.state[q][k].cpu()), k
