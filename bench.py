@@ -287,7 +287,7 @@ def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, de
     return last
 
 
-def timed(fn, device):
+def timed(fn, device, wait_writeback=None):
     """Returns (event ms on the launching stream, host wall ms until ``fn`` returned,
     drain ms, fn's result).  Bracketed by barrier + synchronize on both sides.  The
     drain is what was still running on other streams when the launching stream was
@@ -303,6 +303,8 @@ def timed(fn, device):
     wall = time.perf_counter() - t0
     e1.synchronize()
     t1 = time.perf_counter()
+    if wait_writeback is not None:
+        wait_writeback()  # also waits for write-backs a helper thread has not issued yet
     torch.cuda.synchronize()
     drain = time.perf_counter() - t1
     dist.barrier()
@@ -352,7 +354,8 @@ def main():
         launches0 = C.launch_count()
     exposed = []
     ms, wall_ms, drain_ms, _ = timed(lambda: run_steps(args.steps, ga, opt, loss_fn, batches_dev=dev_batches,
-                                                       exposed=exposed), device)
+                                                       exposed=exposed), device,
+                                     getattr(opt, "wait_writeback", None))
     launches = (C.launch_count() - launches0) if launches0 is not None else None
     clocks = sampler.stop()
     exposed_ms = statistics.mean(a.elapsed_time(b) for a, b in exposed) if exposed else None
@@ -381,7 +384,8 @@ def main():
         host_times = [] if args.verbose > 2 else None
         ms2, wall2, drain2, last_loss = timed(lambda: run_steps(args.steps, ga, opt, loss_fn, host_times=host_times,
                                                         batches_host=host_batches, device=device,
-                                                        read_loss=read_loss), device)
+                                                        read_loss=read_loss), device,
+                                              getattr(opt, "wait_writeback", None))
         ms2 = max_over_ranks(max(ms2, 0.0), device)
         wall2 = max_over_ranks(wall2, device)
         # the loss read-back makes the host wait for the device, so the wall time until

@@ -241,7 +241,7 @@ struct PyArena {
 // ---------------------------------------------------------------------------
 struct PyEngine {
   std::unique_ptr<oab::OffloadEngine> eng;
-  Tensor workspace;  // keeps the slot ring alive
+  Tensor workspace;  // keeps the staging buffer alive
   PyEngine(int64_t device, int64_t compute, int64_t h2d, int64_t d2h, Tensor ws, int64_t chunk_elems,
            int64_t max_ctas, int64_t n_tensors, bool async_writeback)
       : workspace(std::move(ws)) {
@@ -347,6 +347,7 @@ struct PyEngine {
   int64_t prefetched_bytes() const { return eng->prefetched_bytes(); }
   int64_t ring_bytes() const { return (int64_t)eng->ring_bytes(); }
   void synchronize() { py::gil_scoped_release nogil; eng->synchronize(); }
+  void wait_writebacks() { py::gil_scoped_release nogil; eng->wait_writebacks(); }
   int64_t bytes_h2d() const { return eng->bytes_h2d(); }
   int64_t bytes_d2h() const { return eng->bytes_d2h(); }
   void reset_counters() { eng->reset_counters(); }
@@ -409,6 +410,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("join", &PyEngine::join)
       .def("join_compute", &PyEngine::join_compute)
       .def("discard_prefetched", &PyEngine::discard_prefetched)
+      .def("wait_writebacks", &PyEngine::wait_writebacks)
       .def("start_prefetch", &PyEngine::start_prefetch)
       .def("stop_prefetch", &PyEngine::stop_prefetch)
       .def("prefetched_chunks", &PyEngine::prefetched_chunks)

@@ -500,6 +500,11 @@ void OffloadEngine::join_compute(cudaStream_t stream) {
   check(cudaStreamWaitEvent(stream, join_ev_[0], 0), "wait join");
 }
 
+void OffloadEngine::wait_writebacks() {
+  drain_writer();
+  check(cudaStreamSynchronize(d2h_), "sync d2h");
+}
+
 void OffloadEngine::synchronize() {
   stop_prefetch();
   drain_writer();

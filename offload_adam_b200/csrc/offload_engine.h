@@ -115,8 +115,12 @@ class OffloadEngine {
   // Makes `stream` wait for the kernels enqueued so far (parameters are updated) but
   // not for the trailing D2H write-backs of the state.
   void join_compute(cudaStream_t stream);
-  // Blocks the host until the engine streams are idle.
+  // Blocks the host until the engine streams are idle (stops the prefetch thread,
+  // issues every pending write-back first).
   void synchronize();
+  // Blocks the host until the state of every step enqueued so far is back in host
+  // memory; early loads keep running.
+  void wait_writebacks();
 
   int64_t bytes_h2d() const { return bytes_h2d_; }
   int64_t bytes_d2h() const { return bytes_d2h_; }

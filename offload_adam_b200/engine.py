@@ -6,8 +6,10 @@ lives in pinned host memory meets the gradient on the GPU:
 ``zero_copy``  the step kernel reads and writes the mapped host buffers itself,
                over PCIe, in one launch per tensor; no staging memory.
 ``staged``     the C++ copy engine (csrc/offload_engine.cpp) cuts a tensor into
-               chunks and pipelines H2D -> kernel -> D2H through a ring of
-               device slots on three streams.
+               chunks and pipelines H2D -> kernel -> D2H through a circular
+               staging buffer in device memory on three streams; helper threads
+               load the next step's state ahead of time and issue the
+               write-backs.
 ``host``       CPU tensors: everything is synchronous PyTorch (unit tests,
                gloo multi-process tests).
 
@@ -32,7 +34,8 @@ from .ops.oracle import MODE_IDS, beta_hat
 
 class TransferEngine:
     def __init__(self, device, mode, n_tensors, transfer="auto", chunk_elems=8 << 20, ring_slots=4,
-                 max_ctas=0, max_inflight_bytes=8 << 30, staging_bytes=0, async_writeback=True):
+                 max_ctas=0, max_inflight_bytes=8 << 30, staging_bytes=0, async_writeback=True,
+                 serialize=False):
         self.device = torch.device(device)
         self.mode = mode
         self.mode_id = MODE_IDS[mode]
@@ -40,7 +43,7 @@ class TransferEngine:
         if not self.cuda:
             transfer = "host"
         elif transfer == "auto":
-            # measured on B200 over PCIe 5 x16: DMA through the slot ring sustains ~45 GB/s
+            # measured on B200 over PCIe 5 x16: DMA through the staging buffer sustains ~45 GB/s
             # per direction for the step, the zero-copy kernel ~16-40 GB/s
             transfer = "staged"
         if transfer not in ("zero_copy", "staged", "host"):
@@ -52,6 +55,11 @@ class TransferEngine:
         self._inflight_bytes = 0
         self.h2d_stream = self.d2h_stream = self.opt_stream = None
         self._native = None
+        # debugging aid: every transfer and step completes before the call returns, no
+        # helper threads, no early loads; results must equal the overlapped run bit for bit
+        self.serialize = bool(serialize)
+        if self.serialize:
+            async_writeback = False
         self.chunk_elems = int(chunk_elems)
         self._marks, self._last_marks = [], []
         self.scratch = None
@@ -141,13 +149,30 @@ class TransferEngine:
                 for pid, st in items]
         self._native.start_prefetch(self.mode_id, plan, int(max_inflight))
 
+    def wait_writeback(self):
+        """Block the host until the state of every step enqueued so far is back in host
+        memory; early loads keep running."""
+        if not self.cuda:
+            return
+        if self._native is not None:
+            self._native.wait_writebacks()
+        else:
+            self.opt_stream.synchronize()
+
+    def invalidate_prefetched(self):
+        """The caller is about to change host state behind the engine's back (resume,
+        master reload): wait for everything in flight and drop what was loaded early."""
+        self.synchronize()
+        if self._native is not None:
+            self._native.discard_prefetched()
+
     def stop_prefetch(self):
         if self._native is not None:
             self._native.stop_prefetch()
 
     @property
     def can_prefetch(self):
-        return self._native is not None
+        return self._native is not None and not self.serialize
 
     def prefetch(self, pid, states, host_grad=None, from_off=0, max_chunks=0, max_inflight=0):
         """Start the H2D of a tensor's state ahead of its step (staged transfer only),
@@ -164,7 +189,11 @@ class TransferEngine:
                                      int(max_inflight))
 
     def synchronize(self):
+        """Block the host until everything enqueued so far has finished, including
+        write-backs the helper thread has not issued yet.  Stops the early loads."""
         if self.cuda:
+            if self._native is not None:
+                self._native.synchronize()
             self.opt_stream.synchronize()
             self.h2d_stream.synchronize()
             self.d2h_stream.synchronize()
@@ -213,6 +242,8 @@ class TransferEngine:
                                          sumsq=sumsq, scratch=self.scratch, max_ctas=self.max_ctas,
                                          stream=s, use_cuda=True)
         self._retain(dev_grad, copied_out=True)
+        if self.serialize:
+            self.synchronize()
 
     # ------------------------------------------------------------------- step
     def step(self, pid, param, dev_grad, host_grad, states, hp, step, decoupled, clip=None, seed=0,
@@ -252,6 +283,8 @@ class TransferEngine:
                 use_cuda=self.cuda, g_peers=g_peers, g_scale=g_scale, p_peers=p_peers, status=status,
             )
         self._retain(dev_grad)
+        if self.serialize:
+            self.synchronize()
 
     def bytes_moved(self):
         if self._native is not None:

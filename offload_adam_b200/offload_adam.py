@@ -101,9 +101,17 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             most, a few milliseconds); 0 queues everything that fits in the staging buffer as soon as a step
             ends, which keeps the link busy through the step but makes other H2D copies
             wait behind it.
+        debug_serialize: debugging aid against stream races.  Every transfer and step
+            finishes before the call that enqueued it returns; no helper threads, no early
+            loads.  Results must equal the overlapped run bit for bit; a difference points
+            at a missing dependency between streams.
+        nvtx: wrap ``step()``, the gradient hooks and the clip reduction in NVTX ranges
+            (``oab.*``) for timeline profilers.
         async_writeback: issue the D2H write-backs of the staged transfer from a helper
             thread, so that the caller never blocks on a full stream queue (default).
         chunk_elems: elements per staged chunk (default 8 Mi).
+        ring_slots: smallest number of full-width chunks the staging buffer must hold,
+            whatever ``staging_bytes`` says (default 4).
         staging_bytes: HBM set aside for the circular staging buffer of the staged
             transfer.  State of the first tensors of the next step is brought into it
             while forward/backward run and the last write-backs of a step drain from it
@@ -141,7 +149,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                  prefetch_policy="eager", verbose=0, *, transfer="auto", grad_residency="auto",
                  device_grad_budget=None, chunk_elems=None, ring_slots=4, max_ctas=0,
                  max_inflight_bytes=8 << 30, staging_bytes=None, prefetch_inflight=2, prefetch_pacing="thread", async_writeback=True,
-                 seed=None):
+                 debug_serialize=False, nvtx=False, seed=None):
         if prefetch_policy not in ("eager", "lazy"):
             raise ValueError(f"prefetch_policy must be 'eager' or 'lazy' (got {prefetch_policy!r})")
         if grad_residency not in ("auto", "host", "device"):
@@ -228,6 +236,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             # large chunks: every chunk costs five operations on the D2H stream and a
             # stream takes about a thousand pending operations before enqueueing blocks
             chunk_elems = 8 << 20
+        self._nvtx = bool(nvtx) and self._cuda
         self.prefetch_inflight = int(prefetch_inflight)
         if prefetch_pacing not in ("thread", "hooks"):
             raise ValueError(f"prefetch_pacing must be 'thread' or 'hooks', got {prefetch_pacing!r}")
@@ -236,7 +245,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             self.device, mode, len(params), transfer=transfer, chunk_elems=chunk_elems,
             ring_slots=ring_slots, max_ctas=max_ctas, max_inflight_bytes=max_inflight_bytes,
             staging_bytes=self._resolve_staging_bytes(staging_bytes),
-            async_writeback=async_writeback,
+            async_writeback=async_writeback, serialize=debug_serialize,
         )
         self.transfer = self._engine.transfer
         self.h2d_stream = self._engine.h2d_stream
@@ -421,6 +430,15 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
 
     @torch.no_grad()
     def _grad_hook(self, p):
+        if not self._nvtx:
+            return self._grad_hook_body(p)
+        torch.cuda.nvtx.range_push("oab.grad_hook")
+        try:
+            return self._grad_hook_body(p)
+        finally:
+            torch.cuda.nvtx.range_pop()
+
+    def _grad_hook_body(self, p):
         if p.grad is None:
             return
         self._pace_prefetch(1)
@@ -635,6 +653,15 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
     # -------------------------------------------------------------- public API
     @torch.no_grad()
     def step(self, closure=None):
+        if not self._nvtx:
+            return self._step_body(closure)
+        torch.cuda.nvtx.range_push("oab.step")
+        try:
+            return self._step_body(closure)
+        finally:
+            torch.cuda.nvtx.range_pop()
+
+    def _step_body(self, closure=None):
         if closure is not None:
             raise NotImplementedError(
                 f"{type(self).__name__} does not support closure-based step: gradients are "
@@ -712,7 +739,14 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         self._finish_step()
         self._engine.synchronize()
 
+    def wait_writeback(self):
+        """Block the host until the optimizer state of the last step is back in host
+        memory (it normally drains behind the next forward pass).  Early loads of the
+        next step keep running, unlike with ``synchronize()``."""
+        self._engine.wait_writeback()
+
     def _copy_master(self, p, tensor):
+        self._engine.invalidate_prefetched()  # a copy loaded ahead of time would be stale
         self.state[p]["master_params"].copy_(tensor)
 
     def _tracks(self, p):
@@ -731,6 +765,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         """Resume from ``state_dict()`` output by copying into the existing buffers
         (pinned host tensors stay where they are, dtypes are preserved)."""
         self.synchronize()
+        self._engine.invalidate_prefetched()  # state loaded ahead of time would be stale
         saved_ids = [i for g in state_dict["param_groups"] for i in g["params"]]
         live = [p for g in self.param_groups for p in g["params"]]
         if len(saved_ids) != len(live):

@@ -103,6 +103,7 @@ class DistributedOffloadAdam(OffloadAdam):
         return f"[rank {self._rank}] "
 
     def _copy_master(self, p, tensor):
+        self._engine.invalidate_prefetched()  # a copy loaded ahead of time would be stale
         if p in self._sharded:
             lo, hi = self._rows(p)
             tensor = tensor[lo:hi]
