@@ -243,7 +243,7 @@ def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, de
     """One entry of ``batches_*`` per micro-batch (cycled).  With ``batches_host``
     (end-to-end mode) the token ids of a step are copied from pinned host memory at the
     start of that step, on a side stream as a data loader would, and the step's loss is
-    read back to the host after ``step()``."""
+    read back to the host after its last backward pass."""
     last = None
     k = 0
     copy_stream = torch.cuda.Stream(device) if batches_host is not None else None
@@ -272,16 +272,20 @@ def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, de
             (loss / ga).backward()
             last = loss.detach()
         t_host.append(time.perf_counter())  # forward/backward enqueued
+        if batches_host is not None:
+            # device -> host read of the step's result (4 bytes).  Read where a training
+            # script logs it, before the optimizer step is enqueued: the host then waits
+            # for the backward pass only and enqueues the step and the next forward
+            # while the GPU works, instead of idling until the step has finished.
+            last = read_loss(last)
+        t_host.append(time.perf_counter())  # loss on the host
         if exposed is not None:
             e0 = torch.cuda.Event(enable_timing=True); e0.record()
         opt.step()
-        t_host.append(time.perf_counter())  # step() returned
         if exposed is not None:
             e1 = torch.cuda.Event(enable_timing=True); e1.record()
             exposed.append((e0, e1))
-        if batches_host is not None:
-            last = read_loss(last)  # device -> host read of the step's result (4 bytes)
-        t_host.append(time.perf_counter())
+        t_host.append(time.perf_counter())  # step() returned
         if host_times is not None:
             host_times.append([round((b - a) * 1e3, 1) for a, b in zip(t_host, t_host[1:])])
     return last
@@ -388,11 +392,11 @@ def main():
                                               getattr(opt, "wait_writeback", None))
         ms2 = max_over_ranks(max(ms2, 0.0), device)
         wall2 = max_over_ranks(wall2, device)
-        # the loss read-back makes the host wait for the device, so the wall time until
-        # the last loss is on the host and the event time agree; report the larger
+        # the event time ends when the last step's kernels have run on the launching
+        # stream, the wall time when the host has enqueued it; report the larger
         t = max(ms2, wall2)
         if host_times and rank == 0:
-            print("[rank 0] e2e host ms per step [stage inputs + enqueue fwd/bwd, step(), read loss]:",
+            print("[rank 0] e2e host ms per step [stage inputs + enqueue fwd/bwd, read loss, step()]:",
                   host_times, flush=True)
         e2e = {"value": tokens_per_step * args.steps / (t / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": ga * mb * seq * 8, "d2h_bytes_per_step": 4,
