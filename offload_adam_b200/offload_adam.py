@@ -118,7 +118,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             while the next forward runs, so the host link works through the whole
             iteration instead of only during the exposed part of the step.  ``None``
             (default): this rank's state size, at most a quarter of the device's memory
-            (the same budget rule as ``device_grad_budget``).  A few hundred MB are
+            and a third of the memory that is free when the optimizer is built.  A few hundred MB are
             enough for the step itself; everything above that buys overlap.
         max_ctas: grid cap of the streaming kernels (0: kernel default); small
             values leave the SMs to the concurrent backward GEMMs.
@@ -407,7 +407,10 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         if staging_bytes is None:
             staging_bytes = state
             if self._cuda:
-                staging_bytes = min(state, torch.cuda.get_device_properties(self.device).total_memory // 4)
+                # a quarter of the device, but never more than a third of what is free
+                # now (the model is already resident; activations still need room)
+                free, total = torch.cuda.mem_get_info(self.device)
+                staging_bytes = min(state, total // 4, max(free // 3, 1 << 30))
         return min(int(staging_bytes), state)
 
     def _hp(self, group):
