@@ -242,6 +242,8 @@ struct PyArena {
 struct PyEngine {
   std::unique_ptr<oab::OffloadEngine> eng;
   Tensor workspace;  // keeps the staging buffer alive
+  // the engine (helper threads, copies in flight) must be gone before the buffer is
+  ~PyEngine() { eng.reset(); }
   PyEngine(int64_t device, int64_t compute, int64_t h2d, int64_t d2h, Tensor ws, int64_t chunk_elems,
            int64_t max_ctas, int64_t n_tensors, bool async_writeback)
       : workspace(std::move(ws)) {

@@ -71,6 +71,13 @@ OffloadEngine::~OffloadEngine() {
     wb_cv_.notify_all();
     writer_.join();
   }
+  // copies already enqueued still read and write the staging buffer and the host
+  // state; let them finish before the owner releases either (errors are ignored: at
+  // interpreter shutdown the context may be gone)
+  (void)cudaStreamSynchronize(compute_);
+  (void)cudaStreamSynchronize(h2d_);
+  (void)cudaStreamSynchronize(d2h_);
+  (void)cudaGetLastError();
   for (auto& e : all_events_) cudaEventDestroy(e);
   for (auto& e : host_ready_) if (e) cudaEventDestroy(e);
   for (auto& e : grad_ready_) if (e) cudaEventDestroy(e);

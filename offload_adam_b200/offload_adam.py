@@ -742,6 +742,16 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         self._finish_step()
         self._engine.synchronize()
 
+    def __del__(self):
+        # transfers in flight still touch the pinned state and the staging buffer:
+        # finish them before either is released
+        eng = getattr(self, "_engine", None)
+        if eng is not None:
+            try:
+                eng.synchronize()
+            except Exception:
+                pass
+
     def wait_writeback(self):
         """Block the host until the optimizer state of the last step is back in host
         memory (it normally drains behind the next forward pass).  Early loads of the
