@@ -318,3 +318,31 @@ def test_gpu_early_loads_and_trailing_writebacks_are_exact(pacing, clip, staging
     for p, q in zip(m_a.parameters(), m_b.parameters()):
         for k in ("exp_avg", "exp_avg_sq", "master_params"):
             assert torch.equal(o_a.state[p][k].cpu(), o_b.state[q][k].cpu()), k
+
+
+def test_reference_import_paths_exist():
+    """Module paths a user of the reference package imports from."""
+    import importlib
+    import offload_adam_b200 as pkg
+    for name in ("Adam", "OffloadAdam", "DistributedOffloadAdam"):
+        assert hasattr(pkg, name)
+    kernels = importlib.import_module("offload_adam_b200.kernels")
+    for mode in ("stochastic_rounding", "fp32_master", "fp31_master", "fp32_master_custom_rounding"):
+        fn = getattr(kernels, f"adam_step_{mode}")
+        sub = importlib.import_module(f"offload_adam_b200.kernels.{mode}")
+        assert getattr(sub, f"adam_step_{mode}") is fn
+    pa = importlib.import_module("offload_adam_b200.pinned_alloc")
+    for name in ("zeros_pinned", "resolve_numa_target", "numa_node_free_bytes", "gpu_numa_node"):
+        assert callable(getattr(pa, name))
+    d = importlib.import_module("offload_adam_b200.distributed_offload_adam")
+    assert d.DistributedOffloadAdam is pkg.DistributedOffloadAdam
+    q = importlib.import_module("offload_adam_b200.qweight")
+    for name in ("NVFP4QWeight", "NF4QWeight", "Int4QWeight", "Int8QWeight", "quantize_linears",
+                 "save_quantized_pretrained", "QuantizeReport"):
+        assert hasattr(q, name)
+    # functional step on CPU tensors through the reference-style call
+    p = torch.zeros(8, dtype=torch.bfloat16)
+    st = {"grad": torch.ones(8, dtype=torch.bfloat16), "exp_avg": torch.zeros(8, dtype=torch.bfloat16),
+          "exp_avg_sq": torch.zeros(8, dtype=torch.bfloat16), "master_params": torch.zeros(8)}
+    kernels.adam_step_fp32_master(p, st, 1e-2, 0.0, 0.9, 0.999, 1e-8, 1)
+    assert torch.allclose(st["master_params"], torch.full((8,), -1e-2), atol=1e-6) and p[0].item() < 0
