@@ -36,9 +36,16 @@ def add_common_args(p):
     p.add_argument("--prefetch-policy", choices=["eager", "lazy"], default="eager")
     p.add_argument("--transfer", choices=["auto", "staged", "zero_copy"], default="auto")
     p.add_argument("--grad-residency", choices=["auto", "host", "device"], default="auto")
+    p.add_argument("--staging-gib", type=float, default=None,
+                   help="device staging buffer of the offloaded optimizers in GiB (default: the state "
+                        "size, at most a quarter of the GPU); smaller saves memory, larger hides more PCIe time")
     p.add_argument("--gradient-checkpointing", action="store_true")
     p.add_argument("--seed", type=int, default=1234)
     p.add_argument("--json-output", type=Path)
+
+
+def staging_arg(args):
+    return None if args.staging_gib is None else int(args.staging_gib * 2**30)
 
 
 def numa_arg(v):

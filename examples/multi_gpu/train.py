@@ -43,7 +43,8 @@ def main():
         model, lr=args.lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=args.weight_decay, mode=args.mode,
         decoupled_weight_decay=True, max_grad_norm=args.max_grad_norm, numa_node=common.numa_arg(args.numa_node),
         prefetch_policy=args.prefetch_policy, verbose=1, transfer=args.transfer,
-        grad_residency=args.grad_residency, comm=args.comm, seed=args.seed)
+        grad_residency=args.grad_residency, comm=args.comm, seed=args.seed,
+        staging_bytes=common.staging_arg(args))
     if rank == 0:
         print(f"model={args.model_name} world_size={world} device={torch.cuda.get_device_name(local_rank)} "
               f"mode={args.mode} comm={opt.comm}", flush=True)

@@ -61,7 +61,8 @@ def main():
     if args.enable_offloading:
         opt = OffloadAdam(model, numa_node=common.numa_arg(args.numa_node), verbose=1,
                           max_grad_norm=args.max_grad_norm, prefetch_policy=args.prefetch_policy,
-                          transfer=args.transfer, grad_residency=args.grad_residency, **hp)
+                          transfer=args.transfer, grad_residency=args.grad_residency,
+                          staging_bytes=common.staging_arg(args), **hp)
     else:
         opt = Adam(model.parameters(), **hp)
     if args.load_master_from and cls is not None:
