@@ -4,6 +4,7 @@
     python -m offload_adam_b200.utils.microbench staged_step --mode fp32_master --elems 134217728
     python -m offload_adam_b200.utils.microbench accumulate --elems 268435456
     python -m offload_adam_b200.utils.microbench quant --format nvfp4 --rows 14336 --cols 4096
+    python -m offload_adam_b200.utils.microbench peers_step --mode fp32_master --elems 67108864 --world 8
 
 Each case warms up, then times ``--iters`` launches with CUDA events on the launching
 stream (operands are far larger than L2 unless ``--elems`` is made small), and prints one
@@ -74,6 +75,34 @@ def case_adam_step(args):
     nbytes = args.elems * BYTES_PER_ELEM[args.mode]
     peak, src = hbm_peak_gbs()
     return {"case": "adam_step", "mode": args.mode, "elems": args.elems, "ms": best, "ms_avg": avg,
+            "bytes": nbytes, "GBs": nbytes / best / 1e6, "peak_GBs": peak,
+            "fraction_of_%s_hbm_copy" % src: nbytes / best / 1e6 / peak}
+
+
+def case_peers_step(args):
+    """The fused pull + average + Adam + push kernel of the ZeRO-1 path on ONE GPU: the
+    replicas of the other ranks are buffers of the same device (the kernel only sees
+    addresses), so the traffic that would cross NVLink stays in HBM.  Useful for an
+    ``ncu`` capture of the kernel and as an upper bound of its rate."""
+    from ..ops.adam_step import adam_step
+    n, w = args.elems, args.world
+    p, st = make_states(n, args.mode, "cuda")
+    st.pop("grad")
+    grads = [(torch.randn(n, device="cuda") * 1e-2).to(torch.bfloat16) for _ in range(w)]
+    replicas = [p] + [torch.empty_like(p) for _ in range(w - 1)]
+    step = [1]
+
+    def run():
+        step[0] += 1
+        adam_step(args.mode, p, st, 1e-4, 0.01, 0.9, 0.999, 1e-8, step[0], decoupled_weight_decay=True, seed=1,
+                  g_peers=[g.data_ptr() for g in grads], g_scale=1.0 / w,
+                  p_peers=[r.data_ptr() for r in replicas])
+
+    best, avg = timeit(run, args.iters)
+    # per element: w gradients read, state read and written, w parameter replicas written
+    nbytes = n * (BYTES_PER_ELEM[args.mode] - 4 + 2 * w + 2 * w)
+    peak, src = hbm_peak_gbs()
+    return {"case": "peers_step", "mode": args.mode, "elems": n, "world": w, "ms": best, "ms_avg": avg,
             "bytes": nbytes, "GBs": nbytes / best / 1e6, "peak_GBs": peak,
             "fraction_of_%s_hbm_copy" % src: nbytes / best / 1e6 / peak}
 
@@ -169,18 +198,19 @@ def case_quant(args):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("case", choices=["adam_step", "accumulate", "staged_step", "quant"])
+    ap.add_argument("case", choices=["adam_step", "peers_step", "accumulate", "staged_step", "quant"])
     ap.add_argument("--mode", default="fp32_master", choices=list(BYTES_PER_ELEM))
     ap.add_argument("--elems", type=int, default=256 << 20)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--transfer", default="staged", choices=["staged", "zero_copy"])
     ap.add_argument("--chunk-elems", type=int, default=8 << 20)
     ap.add_argument("--ring-slots", type=int, default=4)
+    ap.add_argument("--world", type=int, default=8, help="peers_step: number of (same-device) replicas")
     ap.add_argument("--format", default="nvfp4", choices=["nvfp4", "nf4", "int4", "int8"])
     ap.add_argument("--rows", type=int, default=14336)
     ap.add_argument("--cols", type=int, default=4096)
     args = ap.parse_args()
-    fn = {"adam_step": case_adam_step, "accumulate": case_accumulate, "staged_step": case_staged_step,
+    fn = {"adam_step": case_adam_step, "peers_step": case_peers_step, "accumulate": case_accumulate, "staged_step": case_staged_step,
           "quant": case_quant}[args.case]
     print(json.dumps(fn(args)))
 
