@@ -2,6 +2,7 @@
 
 from .apply import QuantizeReport, quantize_linears, save_quantized_pretrained
 from .base import QWeightBase
+from .fake_quant import fake_quantize
 from .int4 import Int4QWeight
 from .int8 import Int8QWeight
 from .nf4 import NF4QWeight
@@ -16,4 +17,5 @@ __all__ = [
     "quantize_linears",
     "save_quantized_pretrained",
     "QuantizeReport",
+    "fake_quantize",
 ]
