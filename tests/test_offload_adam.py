@@ -346,3 +346,51 @@ def test_reference_import_paths_exist():
           "exp_avg_sq": torch.zeros(8, dtype=torch.bfloat16), "master_params": torch.zeros(8)}
     kernels.adam_step_fp32_master(p, st, 1e-2, 0.0, 0.9, 0.999, 1e-8, 1)
     assert torch.allclose(st["master_params"], torch.full((8,), -1e-2), atol=1e-6) and p[0].item() < 0
+
+
+class Branchy(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a = torch.nn.Linear(32, 64)
+        self.b = torch.nn.Linear(64, 64)
+        self.c = torch.nn.Linear(64, 16)
+        self.unused = torch.nn.Linear(64, 64)
+        self.frozen = torch.nn.Linear(16, 16)
+        for p in self.frozen.parameters():
+            p.requires_grad_(False)
+
+    def forward(self, x, use_b=True):
+        h = torch.relu(self.a(x))
+        if use_b:
+            h = torch.relu(self.b(h))
+        return self.frozen(self.c(h))
+
+
+@pytest.mark.parametrize("clip", [None, 0.05])
+def test_parameters_without_gradient_are_left_alone(clip):
+    """Frozen parameters are not tracked; a trainable parameter that received no gradient
+    in a step keeps its state and its step count (the reference steps it with whatever
+    its gradient buffer holds); a learning-rate schedule is read at every step."""
+    torch.manual_seed(0)
+    m = Branchy().to(torch.bfloat16)
+    opt = OffloadAdam(m, lr=1e-2, mode="fp32_master", max_grad_norm=clip, inplace_param_threshold=100,
+                      weight_decay=0.01, decoupled_weight_decay=True)
+    assert all(p not in opt.state for p in m.frozen.parameters())
+    before_unused = m.unused.weight.detach().clone()
+    before_b = None
+    g = torch.Generator().manual_seed(1)
+    for step in range(4):
+        x = torch.randn(8, 32, generator=g).to(torch.bfloat16)
+        if step == 1:
+            before_b = m.b.weight.detach().clone()
+        opt.ready_for_optimizer_step = True
+        m(x, use_b=step % 2 == 0).float().pow(2).mean().backward()
+        opt.step()
+        if step == 1:
+            assert torch.equal(before_b, m.b.weight)  # no gradient in this step
+        for group in opt.param_groups:
+            group["lr"] *= 0.5
+    opt.synchronize()
+    assert opt.state[m.unused.weight]["step"] == 0 and torch.equal(before_unused, m.unused.weight)
+    assert opt.state[m.b.weight]["step"] == 2 and opt.state[m.a.weight]["step"] == 4
+    assert all(torch.isfinite(p.float()).all() for p in m.parameters())
