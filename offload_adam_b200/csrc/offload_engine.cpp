@@ -49,6 +49,7 @@ OffloadEngine::OffloadEngine(int device, cudaStream_t compute, cudaStream_t h2d,
   wb_submitted_.assign(n_tensors, 0);
   wb_issued_.reset(new std::atomic<int64_t>[n_tensors > 0 ? n_tensors : 1]);
   for (int i = 0; i < n_tensors; ++i) wb_issued_[i].store(0);
+  for (auto& e : wb_throttle_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event");
   if (opt_.async_writeback) writer_ = std::thread([this] { writer_loop(); });
   loader_ = std::thread([this] { loader_loop(); });
 }
@@ -79,6 +80,7 @@ OffloadEngine::~OffloadEngine() {
   (void)cudaStreamSynchronize(d2h_);
   (void)cudaGetLastError();
   for (auto& e : all_events_) cudaEventDestroy(e);
+  for (auto& e : wb_throttle_) if (e) cudaEventDestroy(e);
   for (auto& e : host_ready_) if (e) cudaEventDestroy(e);
   for (auto& e : grad_ready_) if (e) cudaEventDestroy(e);
   if (tmp_ev_) cudaEventDestroy(tmp_ev_);
@@ -142,8 +144,25 @@ void OffloadEngine::writer_loop() {
       wb_q_.pop_front();
       wb_busy_ = true;
     }
+    // throttle: a new group of jobs may start once the group issued kWbGroups groups
+    // earlier has completed on the device (poll and sleep, never block in the driver)
+    const int group = (int)((wb_jobs_ / kWbGroup) % kWbGroups);
+    if (wb_jobs_ % kWbGroup == 0 && wb_throttle_used_[group]) {
+      for (;;) {
+        const cudaError_t q = cudaEventQuery(wb_throttle_[group]);
+        if (q != cudaErrorNotReady) break;  // done (or failed: the issue below reports it)
+        (void)cudaGetLastError();
+        std::this_thread::sleep_for(std::chrono::microseconds(100));
+      }
+      (void)cudaGetLastError();
+      wb_throttle_used_[group] = false;
+    }
     cudaError_t e = cudaSuccess;
-    issue_writeback(j, &e);  // may block while the stream's queue is full: that is the point
+    issue_writeback(j, &e);
+    if (wb_jobs_ % kWbGroup == kWbGroup - 1 && e == cudaSuccess &&
+        cudaEventRecord(wb_throttle_[group], d2h_) == cudaSuccess)
+      wb_throttle_used_[group] = true;
+    ++wb_jobs_;
     {
       std::lock_guard<std::mutex> lk(wb_mu_);
       wb_busy_ = false;

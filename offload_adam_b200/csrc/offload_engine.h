@@ -199,6 +199,14 @@ class OffloadEngine {
   bool pf_has_plan_ = false, pf_running_ = false, pf_exit_ = false;
   std::atomic<bool> pf_stop_{false}, pf_active_{false};
   std::string pf_error_;
+  // The helper thread keeps at most kWbGroups * kWbGroup chunks (about 500 stream
+  // operations, half of what a stream takes) pending on the D2H stream and sleeps
+  // between polls when that many are: it must never sit inside a blocking enqueue call,
+  // which would hold up launches of the other threads as well.
+  static constexpr int kWbGroup = 8, kWbGroups = 12;
+  cudaEvent_t wb_throttle_[kWbGroups] = {};
+  bool wb_throttle_used_[kWbGroups] = {};
+  int64_t wb_jobs_ = 0;  // jobs issued by the helper thread
   std::vector<int64_t> wb_submitted_;                  // per tensor, by the caller
   std::unique_ptr<std::atomic<int64_t>[]> wb_issued_;  // per tensor, by the helper thread
 };
