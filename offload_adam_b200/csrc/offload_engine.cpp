@@ -346,7 +346,7 @@ void OffloadEngine::loader_loop() {
           bool full = false;
           const int64_t now = prefetch_impl(a, off, 0, inflight, &full);
           if (full) { done = true; break; }
-          if (now == off) std::this_thread::sleep_for(std::chrono::microseconds(50));
+          if (now == off) std::this_thread::sleep_for(std::chrono::microseconds(200));
           off = now;
         }
       }

@@ -88,7 +88,7 @@ class OffloadEngine {
                    bool* full);
   // The same early H2D, driven by a helper thread instead of by calls from the
   // training loop: the thread walks `items` in order and keeps `max_inflight` chunk
-  // copies outstanding (polling their events between short sleeps) until the staging
+  // copies outstanding (polling their events every 200 us) until the staging
   // buffer is full, the plan is done or stop_prefetch() is called.  Pacing then does
   // not depend on where the host thread is relative to the GPU.  Between
   // start_prefetch() and stop_prefetch() the helper thread owns the staging buffer;
