@@ -460,6 +460,7 @@ void OffloadEngine::staged_step(const StagedStepArgs& a) {
 
 void OffloadEngine::staged_grad_to_host(int pid, void* host_grad, const void* dev_grad, int64_t n,
                                         bool first, float* sumsq_out, float* scratch) {
+  stop_prefetch();  // this call allocates staging space on the caller's thread
   const bool tracked = pid >= 0 && pid < (int)grad_ready_.size();
   const int64_t C = opt_.chunk_elems;
   if (first && sumsq_out == nullptr) {

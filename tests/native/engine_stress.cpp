@@ -1,0 +1,197 @@
+// Stress test of the copy engine's host-side logic on the CPU: the real
+// offload_engine.cpp is compiled against the stand-in runtime in fake_cuda/ (streams are
+// threads with random delays and bounded queues) and a stand-in "kernel" that adds
+// known constants to every element it is given.  After S steps every element of the
+// host state must hold its initial value plus S times the constants: a chunk that was
+// stepped twice or not at all, loaded before its previous write-back had finished,
+// overwritten in the staging buffer before it was written back, or mixed up with
+// another tensor shows up as a wrong value.  Built with -fsanitize=thread the same run
+// checks the helper threads' use of the engine's data structures.
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <random>
+#include <vector>
+
+#include "../../offload_adam_b200/csrc/offload_engine.cpp"
+
+namespace oab {
+// stand-in kernel: m += 1, v += 2, extra(fp32) += 3 + g, p = m
+cudaError_t launch_adam_step(const AdamStepArgs& a, cudaStream_t s) {
+  AdamStepArgs c = a;
+  s->push([c] {
+    uint16_t* m = static_cast<uint16_t*>(c.m);
+    uint16_t* v = static_cast<uint16_t*>(c.v);
+    float* x = static_cast<float*>(c.extra);
+    const uint16_t* g = static_cast<const uint16_t*>(c.g);
+    uint16_t* p = static_cast<uint16_t*>(c.p);
+    for (int64_t i = 0; i < c.n; ++i) {
+      m[i] = (uint16_t)(m[i] + 1);
+      v[i] = (uint16_t)(v[i] + 2);
+      if (x) x[i] += 3.0f + (g ? (float)g[i] : 0.0f);
+      if (p) p[i] = m[i];
+    }
+  });
+  return cudaSuccess;
+}
+// stand-in accumulate: out = a + b (uint16 arithmetic)
+cudaError_t launch_grad_accumulate(const AccumArgs& a, cudaStream_t s) {
+  AccumArgs c = a;
+  s->push([c] {
+    uint16_t* out = static_cast<uint16_t*>(c.out);
+    const uint16_t* x = static_cast<const uint16_t*>(c.a);
+    const uint16_t* y = static_cast<const uint16_t*>(c.b);
+    for (int64_t i = 0; i < c.n; ++i) out[i] = (uint16_t)(x[i] + (y ? y[i] : 0));
+  });
+  return cudaSuccess;
+}
+}  // namespace oab
+
+using oab::OffloadEngine;
+
+struct Tensor {
+  int64_t n;
+  std::vector<uint16_t> m, v, p, g, hg;  // m, v: host state; p, g: "device"; hg: host gradient
+  std::vector<float> x;
+  std::vector<uint16_t> m0, v0;
+  std::vector<float> x0;
+};
+
+static uint16_t seed_val(int pid, int64_t i, int salt) { return (uint16_t)((pid * 131 + i * 7 + salt * 1009) & 0x3fff); }
+
+struct Scenario {
+  const char* name;
+  int tensors, steps;
+  int64_t chunk;
+  double ring_fraction;  // staging buffer as a fraction of the whole state (<= 0: the minimum)
+  bool async_writeback, thread_prefetch, call_prefetch, shuffle_order;
+  size_t queue_capacity;
+  bool host_grads = false;  // gradients live on the host and are loaded with the state
+};
+
+static int run(const Scenario& sc, unsigned seed) {
+  fake_cuda::queue_capacity = sc.queue_capacity;
+  std::mt19937 rng(seed);
+  std::vector<Tensor> ts(sc.tensors);
+  size_t state_bytes = 0;
+  for (int t = 0; t < sc.tensors; ++t) {
+    Tensor& T = ts[t];
+    T.n = 1 + rng() % (5 * sc.chunk);  // ragged: several chunks and a tail
+    T.m.resize(T.n); T.v.resize(T.n); T.x.resize(T.n); T.p.assign(T.n, 0); T.g.resize(T.n); T.hg.assign(T.n, 0);
+    for (int64_t i = 0; i < T.n; ++i) {
+      T.m[i] = seed_val(t, i, 1); T.v[i] = seed_val(t, i, 2); T.x[i] = (float)seed_val(t, i, 3);
+      T.g[i] = (uint16_t)((t * 7 + i) % 5);
+    }
+    T.m0 = T.m; T.v0 = T.v; T.x0 = T.x;
+    state_bytes += T.n * 8;
+  }
+  fake_cuda::Stream compute(seed + 1), h2d(seed + 2), d2h(seed + 3);
+  oab::EngineOptions opt;
+  opt.chunk_elems = sc.chunk;
+  opt.async_writeback = sc.async_writeback;
+  size_t ring = OffloadEngine::min_ring_bytes(sc.chunk);
+  if (sc.ring_fraction > 0) ring = std::max(ring, (size_t)(state_bytes * sc.ring_fraction) / 256 * 256);
+  void* ws = aligned_alloc(256, ring);
+  int bad = 0;
+  {
+    OffloadEngine eng(0, &compute, &h2d, &d2h, ws, ring, opt, sc.tensors);
+    std::vector<int> order(sc.tensors);
+    for (int t = 0; t < sc.tensors; ++t) order[t] = t;
+    for (int step = 0; step < sc.steps; ++step) {
+      // "forward/backward": time for the early loads of this step
+      std::this_thread::sleep_for(std::chrono::microseconds(rng() % 3000));
+      if (sc.call_prefetch) {  // loads issued from the training thread, a few chunks at a time
+        for (int t = 0; t < sc.tensors; ++t) {
+          oab::StagedStepArgs a;
+          a.pid = t; a.k.mode = oab::kModeFP32Master; a.k.n = ts[t].n;
+          a.k.m = ts[t].m.data(); a.k.v = ts[t].v.data(); a.k.extra = ts[t].x.data();
+          bool full = false;
+          int64_t off = 0;
+          while (off < ts[t].n && !full) {
+            int64_t now = eng.prefetch(a, off, 1 + rng() % 2, 1 + rng() % 2, &full);
+            if (now == off) std::this_thread::sleep_for(std::chrono::microseconds(50));
+            off = now;
+          }
+          if (full) break;
+        }
+      }
+      std::vector<int> step_order = order;
+      if (sc.shuffle_order && step % 2 == 1) std::shuffle(step_order.begin(), step_order.end(), rng);
+      if (sc.host_grads)  // what the gradient hooks of the last micro-batch do
+        for (int t = 0; t < sc.tensors; ++t)
+          eng.staged_grad_to_host(t, ts[t].hg.data(), ts[t].g.data(), ts[t].n, /*first=*/true, nullptr, nullptr);
+      for (int t : step_order) {
+        Tensor& T = ts[t];
+        oab::StagedStepArgs a;
+        a.pid = t;
+        a.k.mode = oab::kModeFP32Master;
+        a.k.n = T.n;
+        a.k.p = T.p.data();
+        if (sc.host_grads) a.host_grad = T.hg.data();
+        else a.k.g = T.g.data();
+        a.k.m = T.m.data(); a.k.v = T.v.data(); a.k.extra = T.x.data();
+        eng.staged_step(a);
+      }
+      eng.join_compute(&compute);
+      if (rng() % 4 == 0) eng.wait_writebacks();
+      if (rng() % 7 == 0) eng.synchronize();
+      if (rng() % 9 == 0) eng.join(&compute);
+      if (sc.thread_prefetch) {  // plan for the next step, as the optimizer hands it over
+        std::vector<OffloadEngine::PrefetchItem> plan;
+        for (int t : order) {
+          OffloadEngine::PrefetchItem it;
+          it.pid = t; it.mode = oab::kModeFP32Master; it.n = ts[t].n;
+          it.m = ts[t].m.data(); it.v = ts[t].v.data(); it.extra = ts[t].x.data();
+          plan.push_back(it);
+        }
+        eng.start_prefetch(plan, 1 + rng() % 3);
+      }
+    }
+    // gradient round trip through the buffer, mixed with whatever is still in flight
+    for (int t = 0; t < sc.tensors; ++t) {
+      eng.staged_grad_to_host(t, ts[t].hg.data(), ts[t].g.data(), ts[t].n, /*first=*/true, nullptr, nullptr);
+      eng.staged_grad_to_host(t, ts[t].hg.data(), ts[t].g.data(), ts[t].n, /*first=*/false, nullptr, nullptr);
+    }
+    eng.synchronize();
+    for (int t = 0; t < sc.tensors; ++t) {
+      const Tensor& T = ts[t];
+      for (int64_t i = 0; i < T.n; ++i) {
+        const uint16_t wm = (uint16_t)(T.m0[i] + sc.steps), wv = (uint16_t)(T.v0[i] + 2 * sc.steps);
+        const float wx = T.x0[i] + (3.0f + (float)T.g[i]) * sc.steps;
+        if (T.m[i] != wm || T.v[i] != wv || T.x[i] != wx || T.p[i] != wm || T.hg[i] != (uint16_t)(2 * T.g[i])) {
+          // (the final gradient round trip leaves hg = g + g in every scenario)
+          if (bad < 5)
+            fprintf(stderr, "%s: tensor %d elem %lld: m %u/%u v %u/%u x %g/%g p %u hg %u/%u\n", sc.name, t,
+                    (long long)i, T.m[i], wm, T.v[i], wv, T.x[i], wx, T.p[i], T.hg[i], 2 * T.g[i]);
+          ++bad;
+        }
+      }
+    }
+  }
+  free(ws);
+  printf("%-28s seed %u: %s (%ld stream operations)\n", sc.name, seed, bad ? "FAILED" : "ok",
+         fake_cuda::ops_executed.load());
+  return bad;
+}
+
+int main(int argc, char** argv) {
+  const int rounds = argc > 1 ? atoi(argv[1]) : 3;
+  const Scenario scenarios[] = {
+      //  name                     tensors steps chunk ring  async thread call  shuffle capacity
+      {"large ring, inline",            6, 4,   64, 2.0,  false, false, false, false, 64},
+      {"minimal ring, inline",          6, 4,   64, 0.0,  false, false, false, false, 64},
+      {"minimal ring, writer thread",   6, 5,   64, 0.0,  true,  false, false, false, 16},
+      {"half ring, both threads",       9, 6,   64, 0.5,  true,  true,  false, false, 16},
+      {"full ring, both threads",       9, 6,   64, 1.1,  true,  true,  false, false, 24},
+      {"small ring, both threads",      9, 6,   32, 0.15, true,  true,  false, false, 8},
+      {"loads from training thread",    7, 5,   64, 0.6,  true,  false, true,  false, 32},
+      {"out-of-order steps",            7, 6,   64, 0.7,  true,  true,  false, true,  32},
+      {"host gradients",                6, 5,   64, 0.3,  true,  true,  false, false, 16, true},
+      {"many chunks, tiny queues",     12, 8,   16, 0.4,  true,  true,  false, false, 6},
+  };
+  int bad = 0;
+  for (int r = 0; r < rounds; ++r)
+    for (const Scenario& sc : scenarios) bad += run(sc, 1000u * r + 17u);
+  printf(bad ? "FAILED\n" : "all scenarios ok\n");
+  return bad ? 1 : 0;
+}
