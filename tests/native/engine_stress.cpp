@@ -67,6 +67,7 @@ struct Scenario {
   bool async_writeback, thread_prefetch, call_prefetch, shuffle_order;
   size_t queue_capacity;
   bool host_grads = false;  // gradients live on the host and are loaded with the state
+  bool destroy_busy = false;  // destroy the engine with transfers in flight: its destructor must finish them
 };
 
 static int run(const Scenario& sc, unsigned seed) {
@@ -152,19 +153,19 @@ static int run(const Scenario& sc, unsigned seed) {
       eng.staged_grad_to_host(t, ts[t].hg.data(), ts[t].g.data(), ts[t].n, /*first=*/true, nullptr, nullptr);
       eng.staged_grad_to_host(t, ts[t].hg.data(), ts[t].g.data(), ts[t].n, /*first=*/false, nullptr, nullptr);
     }
-    eng.synchronize();
-    for (int t = 0; t < sc.tensors; ++t) {
-      const Tensor& T = ts[t];
-      for (int64_t i = 0; i < T.n; ++i) {
-        const uint16_t wm = (uint16_t)(T.m0[i] + sc.steps), wv = (uint16_t)(T.v0[i] + 2 * sc.steps);
-        const float wx = T.x0[i] + (3.0f + (float)T.g[i]) * sc.steps;
-        if (T.m[i] != wm || T.v[i] != wv || T.x[i] != wx || T.p[i] != wm || T.hg[i] != (uint16_t)(2 * T.g[i])) {
-          // (the final gradient round trip leaves hg = g + g in every scenario)
-          if (bad < 5)
-            fprintf(stderr, "%s: tensor %d elem %lld: m %u/%u v %u/%u x %g/%g p %u hg %u/%u\n", sc.name, t,
-                    (long long)i, T.m[i], wm, T.v[i], wv, T.x[i], wx, T.p[i], T.hg[i], 2 * T.g[i]);
-          ++bad;
-        }
+    if (!sc.destroy_busy) eng.synchronize();
+  }
+  for (int t = 0; t < sc.tensors; ++t) {
+    const Tensor& T = ts[t];
+    for (int64_t i = 0; i < T.n; ++i) {
+      const uint16_t wm = (uint16_t)(T.m0[i] + sc.steps), wv = (uint16_t)(T.v0[i] + 2 * sc.steps);
+      const float wx = T.x0[i] + (3.0f + (float)T.g[i]) * sc.steps;
+      if (T.m[i] != wm || T.v[i] != wv || T.x[i] != wx || T.p[i] != wm || T.hg[i] != (uint16_t)(2 * T.g[i])) {
+        // (the final gradient round trip leaves hg = g + g in every scenario)
+        if (bad < 5)
+          fprintf(stderr, "%s: tensor %d elem %lld: m %u/%u v %u/%u x %g/%g p %u hg %u/%u\n", sc.name, t,
+                  (long long)i, T.m[i], wm, T.v[i], wv, T.x[i], wx, T.p[i], T.hg[i], 2 * T.g[i]);
+        ++bad;
       }
     }
   }
@@ -188,6 +189,7 @@ int main(int argc, char** argv) {
       {"out-of-order steps",            7, 6,   64, 0.7,  true,  true,  false, true,  32},
       {"host gradients",                6, 5,   64, 0.3,  true,  true,  false, false, 16, true},
       {"many chunks, tiny queues",     12, 8,   16, 0.4,  true,  true,  false, false, 6},
+      {"destroyed while busy",          8, 4,   64, 0.5,  true,  true,  false, false, 16, false, true},
   };
   int bad = 0;
   for (int r = 0; r < rounds; ++r)
