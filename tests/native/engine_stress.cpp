@@ -51,6 +51,7 @@ using oab::OffloadEngine;
 
 struct Tensor {
   int64_t n;
+  int stepped = 0;  // how many steps this tensor has taken
   std::vector<uint16_t> m, v, p, g, hg;  // m, v: host state; p, g: "device"; hg: host gradient
   std::vector<float> x;
   std::vector<uint16_t> m0, v0;
@@ -68,6 +69,7 @@ struct Scenario {
   size_t queue_capacity;
   bool host_grads = false;  // gradients live on the host and are loaded with the state
   bool destroy_busy = false;  // destroy the engine with transfers in flight: its destructor must finish them
+  bool chaos = false;  // skipped tensors, repeated and cancelled plans, discards between steps
 };
 
 static int run(const Scenario& sc, unsigned seed) {
@@ -123,6 +125,8 @@ static int run(const Scenario& sc, unsigned seed) {
           eng.staged_grad_to_host(t, ts[t].hg.data(), ts[t].g.data(), ts[t].n, /*first=*/true, nullptr, nullptr);
       for (int t : step_order) {
         Tensor& T = ts[t];
+        if (sc.chaos && rng() % 5 == 0) continue;  // no gradient for this tensor in this step
+        ++T.stepped;
         oab::StagedStepArgs a;
         a.pid = t;
         a.k.mode = oab::kModeFP32Master;
@@ -146,6 +150,16 @@ static int run(const Scenario& sc, unsigned seed) {
           plan.push_back(it);
         }
         eng.start_prefetch(plan, 1 + rng() % 3);
+        if (sc.chaos) {
+          switch (rng() % 5) {
+            case 0: eng.stop_prefetch(); break;
+            case 1: eng.discard_prefetched(); break;
+            case 2: eng.start_prefetch(plan, 2); break;  // a second plan replaces the first
+            case 3: std::this_thread::sleep_for(std::chrono::microseconds(300)); eng.discard_prefetched();
+                    eng.start_prefetch(plan, 1); break;
+            default: break;
+          }
+        }
       }
     }
     // gradient round trip through the buffer, mixed with whatever is still in flight
@@ -158,8 +172,9 @@ static int run(const Scenario& sc, unsigned seed) {
   for (int t = 0; t < sc.tensors; ++t) {
     const Tensor& T = ts[t];
     for (int64_t i = 0; i < T.n; ++i) {
-      const uint16_t wm = (uint16_t)(T.m0[i] + sc.steps), wv = (uint16_t)(T.v0[i] + 2 * sc.steps);
-      const float wx = T.x0[i] + (3.0f + (float)T.g[i]) * sc.steps;
+      const uint16_t wm = (uint16_t)(T.m0[i] + T.stepped), wv = (uint16_t)(T.v0[i] + 2 * T.stepped);
+      const float wx = T.x0[i] + (3.0f + (float)T.g[i]) * T.stepped;
+      if (T.stepped == 0 && T.p[i] == 0) continue;  // never stepped: p was never written
       if (T.m[i] != wm || T.v[i] != wv || T.x[i] != wx || T.p[i] != wm || T.hg[i] != (uint16_t)(2 * T.g[i])) {
         // (the final gradient round trip leaves hg = g + g in every scenario)
         if (bad < 5)
@@ -190,6 +205,7 @@ int main(int argc, char** argv) {
       {"host gradients",                6, 5,   64, 0.3,  true,  true,  false, false, 16, true},
       {"many chunks, tiny queues",     12, 8,   16, 0.4,  true,  true,  false, false, 6},
       {"destroyed while busy",          8, 4,   64, 0.5,  true,  true,  false, false, 16, false, true},
+      {"chaos",                         9, 10,  32, 0.6,  true,  true,  false, true,  12, false, false, true},
   };
   int bad = 0;
   for (int r = 0; r < rounds; ++r)
