@@ -252,7 +252,9 @@ def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, de
         t_host = [time.perf_counter()]
         if batches_host is not None:
             staged = []
-            copy_stream.wait_stream(torch.cuda.current_stream(device))
+            # no wait for the main stream: like a data loader, the copies may run while the
+            # previous step is still executing (the destination tensors are new allocations
+            # of the copy stream; the allocator orders their reuse through record_stream)
             with torch.cuda.stream(copy_stream):
                 for micro in range(ga):
                     t = batches_host[(k + micro) % len(batches_host)].to(device, non_blocking=True)
