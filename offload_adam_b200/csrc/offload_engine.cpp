@@ -211,7 +211,8 @@ OffloadEngine::Entry* OffloadEngine::allocate(size_t bytes, bool may_discard) {
       if (!overlaps(e)) break;
       if (e.queued) {
         // its write-back is with the helper thread: it will be issued, wait for that
-        while (!e.retired.load(std::memory_order_acquire)) std::this_thread::yield();
+        while (!e.retired.load(std::memory_order_acquire))
+          std::this_thread::sleep_for(std::chrono::microseconds(20));  // chunks take milliseconds
       }
       if (!e.retired.load(std::memory_order_acquire)) { blocked = true; break; }
     }
@@ -247,7 +248,7 @@ void OffloadEngine::wait_host_copy(const StagedStepArgs& a) {
   if (a.pid >= 0 && a.pid < (int)host_ready_.size() && host_ready_set_[a.pid]) {
     // the event must have been recorded by the helper thread before it can be waited for
     while (wb_issued_[a.pid].load(std::memory_order_acquire) < wb_submitted_[a.pid])
-      std::this_thread::yield();
+      std::this_thread::sleep_for(std::chrono::microseconds(20));
     check(cudaStreamWaitEvent(h2d_, host_ready_[a.pid], 0), "wait host_ready");
   }
   if (a.host_grad && a.pid >= 0 && a.pid < (int)grad_ready_.size() && grad_ready_set_[a.pid])
