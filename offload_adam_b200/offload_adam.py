@@ -19,8 +19,10 @@ How this implementation differs underneath:
   (``utils.pinned_alloc.PinnedArena``) instead of one registration per tensor;
 * the transfer layer (``engine.TransferEngine``) either lets the step kernel
   read/write host memory directly over PCIe (``transfer='zero_copy'``) or
-  pipelines chunks through a device ring (``transfer='staged'``); there is no
-  per-tensor device copy of the state and no host synchronisation;
+  pipelines chunks through a circular staging buffer in device memory
+  (``transfer='staged'``), which also takes in the next step's state while
+  forward/backward run and lets the last step's write-backs drain behind the next
+  forward pass; there is no host synchronisation;
 * gradient accumulation across micro-batches can stay in HBM
   (``grad_residency='device'``; ``'auto'`` picks it when the accumulators fit a
   budget) or live on the host as in the reference (``'host'``), in which case a
