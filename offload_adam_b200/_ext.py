@@ -44,7 +44,8 @@ def sources():
 
 
 def _so_path():
-    cands = glob.glob(os.path.join(_PKG_DIR, _NAME + "*.so"))
+    # the in-tree build writes _C.so, setup.py build_ext --inplace _C.<abi>.so: newest wins
+    cands = sorted(glob.glob(os.path.join(_PKG_DIR, _NAME + "*.so")), key=os.path.getmtime, reverse=True)
     return cands[0] if cands else None
 
 
