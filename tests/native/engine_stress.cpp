@@ -70,6 +70,7 @@ struct Scenario {
   bool host_grads = false;  // gradients live on the host and are loaded with the state
   bool destroy_busy = false;  // destroy the engine with transfers in flight: its destructor must finish them
   bool chaos = false;  // skipped tensors, repeated and cancelled plans, discards between steps
+  int slow_h2d_us = 0, slow_d2h_us = 0;  // extra time per operation of the copy streams
 };
 
 static int run(const Scenario& sc, unsigned seed) {
@@ -89,6 +90,8 @@ static int run(const Scenario& sc, unsigned seed) {
     state_bytes += T.n * 8;
   }
   fake_cuda::Stream compute(seed + 1), h2d(seed + 2), d2h(seed + 3);
+  h2d.extra_delay_us = sc.slow_h2d_us;
+  d2h.extra_delay_us = sc.slow_d2h_us;
   oab::EngineOptions opt;
   opt.chunk_elems = sc.chunk;
   opt.async_writeback = sc.async_writeback;
@@ -206,6 +209,8 @@ int main(int argc, char** argv) {
       {"many chunks, tiny queues",     12, 8,   16, 0.4,  true,  true,  false, false, 6},
       {"destroyed while busy",          8, 4,   64, 0.5,  true,  true,  false, false, 16, false, true},
       {"chaos",                         9, 10,  32, 0.6,  true,  true,  false, true,  12, false, false, true},
+      {"slow write-backs",              8, 5,   64, 1.1,  true,  true,  false, false, 12, false, false, false, 0, 150},
+      {"slow loads",                    8, 5,   64, 0.4,  true,  true,  false, false, 12, false, false, false, 150, 0},
   };
   int bad = 0;
   for (int r = 0; r < rounds; ++r)

@@ -43,6 +43,7 @@ struct Stream {
   std::condition_variable cv_work, cv_space, cv_idle;
   std::deque<std::function<void()>> q;
   bool stop = false, busy = false;
+  int extra_delay_us = 0;  // makes this stream slow relative to the others
   std::thread worker;
   std::mt19937 rng;
   explicit Stream(unsigned seed) : rng(seed) {
@@ -70,6 +71,7 @@ struct Stream {
       cv_space.notify_all();
       const int d = max_delay_us.load();
       if (d > 0) std::this_thread::sleep_for(std::chrono::microseconds(rng() % (unsigned)(d + 1)));
+      if (extra_delay_us > 0) std::this_thread::sleep_for(std::chrono::microseconds(extra_delay_us));
       op();
       ops_executed.fetch_add(1);
       {
