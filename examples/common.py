@@ -14,9 +14,9 @@ import torch
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 from offload_adam_b200.models.llama import (build_llama, llama3_8b, llama3_70b,  # noqa: E402
-                                            tiny_llama)
+                                            qwen3_8b, tiny_llama)
 
-MODELS = {"llama3-8b": llama3_8b, "llama3-70b": llama3_70b, "tiny": tiny_llama}
+MODELS = {"llama3-8b": llama3_8b, "llama3-70b": llama3_70b, "qwen3-8b": qwen3_8b, "tiny": tiny_llama}
 MODES = ["stochastic_rounding", "fp32_master", "fp31_master", "fp32_master_custom_rounding"]
 
 

@@ -38,10 +38,12 @@ class LlamaConfig:
     tie_embeddings: bool = False
     init_std: float = 0.02
     ce_chunk: int = 2048  # rows of the logits computed at a time by the loss head
+    head_dim_override: Optional[int] = None  # Qwen3: 128 whatever hidden_size / num_heads is
+    qk_norm: bool = False  # Qwen3: RMSNorm over head_dim on queries and keys before RoPE
 
     @property
     def head_dim(self):
-        return self.hidden_size // self.num_heads
+        return self.head_dim_override or self.hidden_size // self.num_heads
 
 
 def llama3_8b(**kw) -> LlamaConfig:
@@ -50,6 +52,16 @@ def llama3_8b(**kw) -> LlamaConfig:
 
 def llama3_70b(**kw) -> LlamaConfig:
     base = dict(hidden_size=8192, intermediate_size=28672, num_layers=80, num_heads=64, num_kv_heads=8)
+    base.update(kw)
+    return LlamaConfig(**base)
+
+
+def qwen3_8b(**kw) -> LlamaConfig:
+    """Qwen3-8B shape, the model of the reference's published tables (reference:
+    examples/e2e_train/README.md:36-54): 36 layers, hidden 4096, 32 query / 8 KV heads
+    of 128, SwiGLU 12288, vocabulary 151936, RoPE theta 1e6, RMSNorm on q and k."""
+    base = dict(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_layers=36, num_heads=32,
+                num_kv_heads=8, rope_theta=1e6, rms_eps=1e-6, head_dim_override=128, qk_norm=True)
     base.update(kw)
     return LlamaConfig(**base)
 
@@ -96,11 +108,19 @@ class Attention(nn.Module):
         self.k_proj = nn.Linear(h, self.nkv * d, bias=False)
         self.v_proj = nn.Linear(h, self.nkv * d, bias=False)
         self.o_proj = nn.Linear(self.nh * d, h, bias=False)
+        if cfg.qk_norm:  # parameter names as in HF Qwen3: self_attn.q_norm / k_norm
+            self.q_norm = RMSNorm(d, cfg.rms_eps)
+            self.k_norm = RMSNorm(d, cfg.rms_eps)
+        else:
+            self.q_norm = self.k_norm = None
 
     def forward(self, x, cos, sin):
         B, S, _ = x.shape
-        q = self.q_proj(x).view(B, S, self.nh, self.hd).transpose(1, 2)
-        k = self.k_proj(x).view(B, S, self.nkv, self.hd).transpose(1, 2)
+        q = self.q_proj(x).view(B, S, self.nh, self.hd)
+        k = self.k_proj(x).view(B, S, self.nkv, self.hd)
+        if self.q_norm is not None:
+            q, k = self.q_norm(q), self.k_norm(k)
+        q, k = q.transpose(1, 2), k.transpose(1, 2)
         v = self.v_proj(x).view(B, S, self.nkv, self.hd).transpose(1, 2)
         q = _apply_rope(q, cos, sin)
         k = _apply_rope(k, cos, sin)

@@ -394,3 +394,28 @@ def test_parameters_without_gradient_are_left_alone(clip):
     assert opt.state[m.unused.weight]["step"] == 0 and torch.equal(before_unused, m.unused.weight)
     assert opt.state[m.b.weight]["step"] == 2 and opt.state[m.a.weight]["step"] == 4
     assert all(torch.isfinite(p.float()).all() for p in m.parameters())
+
+
+def test_qwen3_shape_builds_and_trains_a_step():
+    """The model of the reference's published tables: head_dim independent of hidden
+    size, RMSNorm on queries and keys (HF parameter names)."""
+    from offload_adam_b200.models.llama import qwen3_8b
+    full = qwen3_8b()
+    assert (full.head_dim, full.num_layers, full.vocab_size, full.qk_norm) == (128, 36, 151936, True)
+    cfg = qwen3_8b(num_layers=2, vocab_size=512, hidden_size=128, intermediate_size=256, num_heads=4,
+                   num_kv_heads=2, head_dim_override=64, ce_chunk=64)
+    m = build_llama(cfg, device="cpu", dtype=torch.bfloat16)
+    names = dict(m.named_parameters())
+    assert names["model.layers.0.self_attn.q_norm.weight"].shape == (64,)
+    assert names["model.layers.1.self_attn.k_norm.weight"].shape == (64,)
+    assert names["model.layers.0.self_attn.q_proj.weight"].shape == (4 * 64, 128)
+    opt = OffloadAdam(m, lr=1e-2, mode="fp32_master", max_grad_norm=1.0, inplace_param_threshold=1024)
+    ids = torch.randint(0, 512, (2, 32))
+    losses = []
+    for _ in range(3):
+        opt.ready_for_optimizer_step = True
+        loss = m(ids, labels=ids)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert losses[-1] < losses[0]
