@@ -283,24 +283,3 @@ def test_row_shards_requantize_to_the_same_bits(fmt, device):
                 view.copy_(part)
     for a, b in zip(whole._payload(), split._payload()):
         assert _same_bits(a, b)
-
-
-# ---------------------------------------------------------------- fake quantization
-@pytest.mark.parametrize("device", ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)])
-@pytest.mark.parametrize("fmt", ["nvfp4", "nf4", "int4", "int8"])
-def test_fake_quantize_is_quantize_then_dequantize_with_straight_through_gradient(fmt, device):
-    from offload_adam_b200.qweight import (Int4QWeight, Int8QWeight, NF4QWeight, NVFP4QWeight,
-                                           fake_quantize)
-    cls = {"nvfp4": NVFP4QWeight, "nf4": NF4QWeight, "int4": Int4QWeight, "int8": Int8QWeight}[fmt]
-    torch.manual_seed(2)
-    x = (torch.randn(64, 256, device=device) * 0.05).to(torch.bfloat16).requires_grad_(True)
-    y = fake_quantize(x, cls)
-    q = cls.from_float(torch.zeros(64, 256, dtype=torch.bfloat16, device=device))
-    q.copy_(x.detach().float() if device == "cuda" else x.detach())
-    assert y.dtype == x.dtype and torch.equal(y, q.dequantize(torch.bfloat16))
-    err = (y.float() - x.detach().float()).abs().max().item()
-    assert 0 < err < 0.05
-    (y.float() * 2).sum().backward()
-    assert torch.equal(x.grad, torch.full_like(x, 2.0))
-    with pytest.raises(ValueError):
-        fake_quantize(torch.randn(4, 7, device=device).to(torch.bfloat16), cls)
