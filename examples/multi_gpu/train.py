@@ -29,6 +29,9 @@ def main():
     common.add_common_args(p)
     p.add_argument("--per-rank-batch-size", type=int, default=1)
     p.add_argument("--comm", choices=["auto", "symm", "nccl"], default="auto")
+    p.add_argument("--grad-layout", choices=["full", "shard"], default="full",
+                   help="'shard': reduce-scatter every micro-batch and accumulate only this rank's rows "
+                        "(gradient memory divided by the world size; uses the torch.distributed collectives)")
     args = p.parse_args()
     common.validate(args)
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -44,7 +47,7 @@ def main():
         decoupled_weight_decay=True, max_grad_norm=args.max_grad_norm, numa_node=common.numa_arg(args.numa_node),
         prefetch_policy=args.prefetch_policy, verbose=1, transfer=args.transfer,
         grad_residency=args.grad_residency, comm=args.comm, seed=args.seed,
-        staging_bytes=common.staging_arg(args))
+        staging_bytes=common.staging_arg(args), grad_layout=args.grad_layout)
     if rank == 0:
         print(f"model={args.model_name} world_size={world} device={torch.cuda.get_device_name(local_rank)} "
               f"mode={args.mode} comm={opt.comm}", flush=True)

@@ -225,7 +225,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                     self._prefetch_module.setdefault(p, m)
 
         # ---- where gradient accumulators live
-        grad_bytes = sum(p.numel() * 2 for p in self._offload_params)
+        grad_bytes = self._grad_accumulator_bytes()
         if grad_residency == "auto":
             if self._cuda:
                 if device_grad_budget is None:
@@ -293,6 +293,10 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         for m in (modules if self.prefetch_pacing == "hooks" else ()):
             if any(p.requires_grad and p not in self._inplace_params for p in m.parameters()):
                 m.register_forward_pre_hook(lambda *_: self._pace_prefetch(1))
+
+    def _grad_accumulator_bytes(self):
+        """Bytes of the bf16 gradient accumulators of the offloaded parameters."""
+        return sum(p.numel() * 2 for p in self._offload_params)
 
     def _state_shape(self, p, key):
         """Shape of one host state tensor (subclasses shard the non-grad ones).  With

@@ -38,11 +38,22 @@ class DistributedOffloadAdam(OffloadAdam):
     """Sharded-state (ZeRO-1) variant of :class:`OffloadAdam`.
 
     Extra keyword-only arguments: ``process_group`` (default: the world group),
-    ``comm`` (``'auto'`` | ``'nccl'`` | ``'symm'``) and ``wait_timeout_ms`` (bound
-    of every device-side wait on a peer in the ``symm`` path).
+    ``comm`` (``'auto'`` | ``'nccl'`` | ``'symm'``), ``wait_timeout_ms`` (bound
+    of every device-side wait on a peer in the ``symm`` path) and ``grad_layout``:
+
+    * ``'full'`` (default, the reference's layout): every rank accumulates the whole
+      gradient over the micro-batches and the ranks are averaged once, on the last one;
+    * ``'shard'``: every micro-batch's gradient of a sharded tensor is averaged over the
+      ranks at once and only this rank's rows are accumulated.  Accumulators (in HBM or
+      in pinned host memory, by ``grad_residency``) shrink by the world size, which is
+      what lets a model whose full-shape gradient does not fit next to its weights (70B
+      on 8 GPUs) train at all; the price is one reduce-scatter per tensor and
+      micro-batch, and a different rounding order (mean over ranks first, then the bf16
+      sum over micro-batches).  Uses the ``torch.distributed`` collectives.
     """
 
-    def __init__(self, model, *, process_group=None, comm="auto", wait_timeout_ms=30000, **kwargs):
+    def __init__(self, model, *, process_group=None, comm="auto", wait_timeout_ms=30000,
+                 grad_layout="full", **kwargs):
         if not dist.is_available() or not dist.is_initialized():
             raise RuntimeError(
                 "DistributedOffloadAdam requires torch.distributed to be initialized; "
@@ -50,6 +61,13 @@ class DistributedOffloadAdam(OffloadAdam):
             )
         if comm not in ("auto", "nccl", "symm"):
             raise ValueError(f"comm must be 'auto', 'nccl' or 'symm' (got {comm!r})")
+        if grad_layout not in ("full", "shard"):
+            raise ValueError(f"grad_layout must be 'full' or 'shard' (got {grad_layout!r})")
+        if grad_layout == "shard":
+            if comm == "symm":
+                raise ValueError("grad_layout='shard' uses the torch.distributed collectives; pass comm='nccl'")
+            comm = "nccl"
+        self.grad_layout = grad_layout
         self._pg = process_group if process_group is not None else dist.group.WORLD
         self._world_size = dist.get_world_size(self._pg)
         self._rank = dist.get_rank(self._pg)
@@ -75,9 +93,21 @@ class DistributedOffloadAdam(OffloadAdam):
         lo, hi = self._rows(p)
         return p.data[lo:hi]
 
+    def _shard_grads(self, p):
+        return self.grad_layout == "shard" and self._is_sharded_shape(p)
+
+    def _grad_accumulator_bytes(self):
+        if self.grad_layout != "shard":
+            return super()._grad_accumulator_bytes()
+        return sum(p.numel() * 2 // (self._world_size if self._is_sharded_shape(p) else 1)
+                   for p in self._offload_params)
+
     def _state_shape(self, p, key):
         if key == "grad":
-            return super()._state_shape(p, key)
+            full = super()._state_shape(p, key)
+            if full == p.shape and self._shard_grads(p):
+                return (p.shape[0] // self._world_size, *p.shape[1:])
+            return full
         if self._is_sharded_shape(p):
             return (p.shape[0] // self._world_size, *p.shape[1:])
         return p.shape
@@ -195,6 +225,8 @@ class DistributedOffloadAdam(OffloadAdam):
         if p.grad is None:
             return
         symm = self._symm is not None and self._symm.handles(p)
+        if self._world_size > 1 and self._shard_grads(p):
+            return self._shard_grad_hook(p, self.ready_for_optimizer_step)
         if not self.ready_for_optimizer_step or self._world_size <= 1:
             if symm:
                 self._pace_prefetch(1)
@@ -234,6 +266,42 @@ class DistributedOffloadAdam(OffloadAdam):
             eng._retain(acc)
         self._dev_grad[p] = red  # reduced gradient (slice for sharded) waits for its step
         if self._step_in_backward:
+            self._step_offload(p, self._param2group[p])
+
+    def _shard_grad_hook(self, p, last):
+        """``grad_layout='shard'``: average this micro-batch's gradient over the ranks
+        now and accumulate only this rank's rows."""
+        grad = self._take_grad(p)
+        st = self.state[p]
+        eng = self._engine
+        s = self._opt_stream_handle()
+        eng.fork_from_main()
+        with self._side():
+            red = self._avg_reduce_scatter(grad, p)
+            total = None
+            if self.grad_residency == "device":
+                acc = self._dev_grad.get(p)
+                if acc is None:
+                    total = red
+                else:
+                    grad_ops.grad_accumulate(acc, acc, red, scratch=eng.scratch, use_cuda=self._cuda, stream=s)
+                    total = acc
+                self._dev_grad[p] = total
+            elif last:
+                if st["host_grad_valid"]:
+                    grad_ops.grad_accumulate(red, red, st["grad"], use_cuda=self._cuda, stream=s)
+                    st["host_grad_valid"] = False
+                total = red
+                self._dev_grad[p] = total
+            if last and self.max_grad_norm is not None:
+                grad_ops.grad_accumulate(None, total, None, sumsq=self._slot(p), scratch=eng.scratch,
+                                         use_cuda=self._cuda, stream=s)
+        if self.grad_residency != "device" and not last:
+            eng.grad_to_host(self._pid[p], st["grad"], red, first=not st["host_grad_valid"])
+            st["host_grad_valid"] = True
+        eng._retain(grad)
+        eng._retain(red)
+        if last and self._step_in_backward:
             self._step_offload(p, self._param2group[p])
 
     def _opt_stream_handle(self):

@@ -310,3 +310,119 @@ def test_sharded_qat_owner_quantizes_and_gathers_packed_rows(fmt):
             a = a.view(torch.uint8) if a.element_size() == 1 else a
             b = b.view(torch.uint8) if b.element_size() == 1 else b
             assert torch.equal(a, b), (fmt, name, "replicas differ")
+
+
+# ------------------------------------------- grad_layout='shard': reduce-scatter every micro-batch
+def _shard_layout_worker(rank, port, residency, clip, ga, steps, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        model = make_net()
+        opt = DistributedOffloadAdam(model, lr=1e-2, weight_decay=0.05, mode="fp32_master", max_grad_norm=clip,
+                                     decoupled_weight_decay=True, inplace_param_threshold=200,
+                                     grad_layout="shard", grad_residency=residency)
+        assert opt.comm == "nccl" and opt.grad_layout == "shard"
+        want_shape = (0,) if residency == "device" else (32, 32)  # half of the 64 rows
+        assert tuple(opt.state[model.a.weight]["grad"].shape) == want_shape
+        if residency == "host":  # the replicated tensor keeps its full-shape buffer
+            assert tuple(opt.state[model.b.weight]["grad"].shape) == (15, 64)
+        data = rank_batches(rank, ga * steps)
+        k = 0
+        for _ in range(steps):
+            for micro in range(ga):
+                opt.ready_for_optimizer_step = micro == ga - 1
+                (model(data[k]).float().pow(2).mean() / ga).backward()
+                k += 1
+            opt.step()
+        opt.synchronize()
+        torch.save({n: p.detach().clone() for n, p in model.named_parameters()},
+                   os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def shard_layout_reference(clip, ga, steps):
+    """Sharded tensors: mean over ranks of every micro-batch (fp32 sum in rank order, one
+    rounding), then the bf16 sum over micro-batches.  Everything else as in the default
+    layout: bf16 sum over micro-batches per rank, then the mean over ranks."""
+    from offload_adam_b200.ops.adam_step import adam_step
+    model = make_net()
+    ref = Adam(model.parameters(), lr=1e-2, weight_decay=0.05, mode="fp32_master", decoupled_weight_decay=True)
+    data = [rank_batches(r, ga * steps) for r in range(WORLD)]
+    sharded = {id(model.a.weight)}
+
+    def mean_over_ranks(parts):
+        f = torch.zeros_like(parts[0], dtype=torch.float32)
+        for g in parts:
+            f = f + g.float()
+        return (f / WORLD).to(torch.bfloat16)
+
+    for s in range(steps):
+        per_rank_micro = []  # [rank][micro] -> list of grads
+        for r in range(WORLD):
+            micro_grads = []
+            for b in data[r][s * ga:(s + 1) * ga]:
+                model.zero_grad()
+                (model(b).float().pow(2).mean() / ga).backward()
+                micro_grads.append([p.grad.detach().clone() for p in model.parameters()])
+            per_rank_micro.append(micro_grads)
+        avg = []
+        for i, p in enumerate(model.parameters()):
+            if id(p) in sharded:
+                acc = None
+                for m in range(ga):
+                    red = mean_over_ranks([per_rank_micro[r][m][i] for r in range(WORLD)])
+                    acc = red if acc is None else (acc.float() + red.float()).to(torch.bfloat16)
+                avg.append(acc)
+            else:
+                per_rank = []
+                for r in range(WORLD):
+                    acc = None
+                    for m in range(ga):
+                        g = per_rank_micro[r][m][i]
+                        acc = g if acc is None else (acc.float() + g.float()).to(torch.bfloat16)
+                    per_rank.append(acc)
+                avg.append(mean_over_ranks(per_rank))
+        coef = None
+        if clip is not None:
+            total = torch.sqrt(sum((g.float() ** 2).sum() for g in avg))
+            coef = torch.clamp(clip / (total + 1e-6), max=1.0).reshape(1)
+        for p, g in zip(model.parameters(), avg):
+            st = ref.state[p]
+            ref._init_state_if_empty(p, st)
+            st["step"] += 1
+            tensors = {k: st[k] for k in ref.config["states"]}
+            tensors["grad"] = g
+            adam_step("fp32_master", p.data, tensors, 1e-2, 0.05, 0.9, 0.999, 1e-8, st["step"],
+                      decoupled_weight_decay=True, clip_coef=coef)
+    return {n: p.detach().clone() for n, p in model.named_parameters()}
+
+
+@pytest.mark.parametrize("residency", ["host", "device"])
+@pytest.mark.parametrize("clip", [None, 0.02])
+def test_shard_gradient_layout_matches_its_restatement(residency, clip):
+    ga, steps = 3, 3
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_shard_layout_worker, args=(free_port(), residency, clip, ga, steps, d), nprocs=WORLD, join=True)
+        got = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(WORLD)]
+    want = shard_layout_reference(clip, ga, steps)
+    for name in want:
+        assert torch.equal(got[0][name], got[1][name]), f"replicas diverged: {name}"
+        if clip is None:
+            assert torch.equal(got[0][name], want[name]), name
+        else:  # the norm is summed in a different order across ranks
+            assert torch.allclose(got[0][name].float(), want[name].float(), atol=2e-3, rtol=0), name
+
+
+def test_shard_gradient_layout_rejects_the_symmetric_path():
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(free_port())
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        with pytest.raises(ValueError, match="grad_layout"):
+            DistributedOffloadAdam(make_net(), grad_layout="shard", comm="symm")
+        with pytest.raises(ValueError, match="grad_layout"):
+            DistributedOffloadAdam(make_net(), grad_layout="rows")
+    finally:
+        dist.destroy_process_group()
