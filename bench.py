@@ -65,6 +65,8 @@ def parse_args():
     ap.add_argument("--transfer", default="auto")
     ap.add_argument("--grad-residency", default="auto")
     ap.add_argument("--comm", default="auto", help="distributed path: auto | symm | nccl")
+    ap.add_argument("--grad-layout", default="full", choices=["full", "shard"],
+                    help="distributed: 'shard' reduce-scatters every micro-batch (70B memory plan)")
     ap.add_argument("--max-ctas", type=int, default=0)
     ap.add_argument("--staging-gib", type=float, default=None, help="size of the staging ring (default: optimizer default)")
     ap.add_argument("--prefetch-inflight", type=int, default=None,
@@ -190,7 +192,7 @@ def build_ours(args, preset, device):
     if args.prefetch_inflight is not None:
         common["prefetch_inflight"] = args.prefetch_inflight
     if preset["optimizer"] == "distributed":
-        opt = DistributedOffloadAdam(model, comm=args.comm, **common)
+        opt = DistributedOffloadAdam(model, comm=args.comm, grad_layout=args.grad_layout, **common)
     else:
         opt = OffloadAdam(model, **common)
 
@@ -425,6 +427,7 @@ def main():
                 "transfer": getattr(opt, "transfer", None),
                 "grad_residency": getattr(opt, "grad_residency", "host (reference)"),
                 "comm": getattr(opt, "comm", None),
+                "grad_layout": getattr(opt, "grad_layout", None),
                 "staging_gib": (getattr(getattr(opt, "_engine", None), "staging_bytes", 0) or 0) / 2**30,
             },
             "exposed_opt_ms": exposed_ms, "peak_gpu_gb": peak_gb, "build_s": t_build,
