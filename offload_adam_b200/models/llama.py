@@ -258,13 +258,18 @@ class LlamaForCausalLM(nn.Module):
 
 
 def build_llama(cfg: LlamaConfig, device="cuda", dtype=torch.bfloat16, seed=0) -> LlamaForCausalLM:
-    """Random-init model (N(0, init_std), norms at 1) created directly on ``device``."""
+    """Random-init model (N(0, init_std), norms at 1) created directly on ``device`` and
+    directly in ``dtype``: no fp32 copy of the weights ever exists (a 70B model would not
+    fit otherwise)."""
     gen_state = torch.random.get_rng_state()
+    default_dtype = torch.get_default_dtype()
     torch.manual_seed(seed)
     try:
+        torch.set_default_dtype(dtype)
         with torch.device(device):
             model = LlamaForCausalLM(cfg)
         model = model.to(dtype)
     finally:
+        torch.set_default_dtype(default_dtype)
         torch.random.set_rng_state(gen_state)
     return model
