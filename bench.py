@@ -61,6 +61,9 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=None, help="debug only: override layer count")
     ap.add_argument("--seq", type=int, default=None)
     ap.add_argument("--ga", type=int, default=None)
+    ap.add_argument("--mb", type=int, default=None, help="micro-batch size per rank")
+    ap.add_argument("--quant", choices=["none", "nvfp4", "nf4", "int4", "int8"], default="none",
+                    help="QAT: weight-only quantized linear layers (lm_head stays dense); needs mode fp32_master")
     ap.add_argument("--mode", default=None)
     ap.add_argument("--transfer", default="auto")
     ap.add_argument("--grad-residency", default="auto")
@@ -179,6 +182,11 @@ def build_ours(args, preset, device):
     model.train()
     if args.grad_ckpt:
         model.gradient_checkpointing_enable()
+    if args.quant != "none":
+        from offload_adam_b200 import qweight
+        cls = {"nvfp4": qweight.NVFP4QWeight, "nf4": qweight.NF4QWeight, "int4": qweight.Int4QWeight,
+               "int8": qweight.Int8QWeight}[args.quant]
+        qweight.quantize_linears(model, cls, skip_patterns=("lm_head",))
     common = dict(lr=preset["lr"], betas=(0.9, 0.999), eps=1e-8, weight_decay=preset["weight_decay"],
                   mode=preset["mode"], decoupled_weight_decay=True, max_grad_norm=preset["max_grad_norm"],
                   verbose=args.verbose, transfer=args.transfer, grad_residency=args.grad_residency,
@@ -225,6 +233,11 @@ def build_reference(args, preset, device):
     model.train()
     if args.grad_ckpt:
         model.gradient_checkpointing_enable()
+    if args.quant != "none":
+        from offload_adam import qweight as rq  # the reference's own formats
+        cls = {"nvfp4": rq.NVFP4QWeight, "nf4": rq.NF4QWeight, "int4": rq.Int4QWeight,
+               "int8": rq.Int8QWeight}[args.quant]
+        rq.quantize_linears(model, cls, skip_patterns=("lm_head",))
     common = dict(lr=preset["lr"], betas=(0.9, 0.999), eps=1e-8, weight_decay=preset["weight_decay"],
                   mode=preset["mode"], decoupled_weight_decay=True, max_grad_norm=preset["max_grad_norm"],
                   verbose=args.verbose)
@@ -322,7 +335,7 @@ def timed(fn, device, wait_writeback=None):
 def main():
     args = parse_args()
     preset = dict(PRESETS[args.preset])
-    for k in ("seq", "ga", "mode"):
+    for k in ("seq", "ga", "mode", "mb"):
         if getattr(args, k) is not None:
             preset[k] = getattr(args, k)
     if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "offload_adam")):
@@ -428,6 +441,7 @@ def main():
                 "grad_residency": getattr(opt, "grad_residency", "host (reference)"),
                 "comm": getattr(opt, "comm", None),
                 "grad_layout": getattr(opt, "grad_layout", None),
+                "quant": args.quant,
                 "staging_gib": (getattr(getattr(opt, "_engine", None), "staging_bytes", 0) or 0) / 2**30,
             },
             "exposed_opt_ms": exposed_ms, "peak_gpu_gb": peak_gb, "build_s": t_build,
