@@ -148,6 +148,10 @@ class DistributedOffloadAdam(OffloadAdam):
             return
         if want == "nccl":
             return
+        if want == "auto" and self._quant_params:
+            # quantized weights take the collective route for their gradients and packed
+            # payloads; a step that mixes both routes is only selected on request
+            return
         from . import symm
 
         try:
