@@ -276,23 +276,24 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         # No module-level backward pre-hooks: the streaming transfer modes have nothing
         # to park on the GPU ahead of a parameter's gradient, and full backward hooks
         # would add an autograd node per leaf-module call.
+        self._hook_handles = []
         for i, p in enumerate(params):
             st = self.state[p]
             st["step"] = 0
             if self.max_grad_norm is not None:
                 st["grad_norm"] = self._norms[i]
             if p in self._inplace_params:
-                p.register_post_accumulate_grad_hook(self._inplace_grad_hook)
+                self._hook_handles.append(p.register_post_accumulate_grad_hook(self._inplace_grad_hook))
             else:
-                p.register_post_accumulate_grad_hook(self._grad_hook)
+                self._hook_handles.append(p.register_post_accumulate_grad_hook(self._grad_hook))
                 st["host_grad_valid"] = False
         # the next forward must see every update even if the caller skipped step()
-        model.register_forward_pre_hook(lambda *_: self._on_forward())
+        self._hook_handles.append(model.register_forward_pre_hook(lambda *_: self._on_forward()))
         # pacing points for the early H2D during forward (plain forward hooks add no
         # autograd nodes); not needed when the helper thread paces
         for m in (modules if self.prefetch_pacing == "hooks" else ()):
             if any(p.requires_grad and p not in self._inplace_params for p in m.parameters()):
-                m.register_forward_pre_hook(lambda *_: self._pace_prefetch(1))
+                self._hook_handles.append(m.register_forward_pre_hook(lambda *_: self._pace_prefetch(1)))
 
     def _grad_accumulator_bytes(self):
         """Bytes of the bf16 gradient accumulators of the offloaded parameters."""
@@ -747,6 +748,16 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         """Block the host until every enqueued transfer and step has finished."""
         self._finish_step()
         self._engine.synchronize()
+
+    def close(self):
+        """Detach from the model: finish everything in flight and remove the hooks, so
+        that gradients reach ``p.grad`` again (for instance before building another
+        optimizer for the same model).  The state stays readable through
+        ``state_dict()``; stepping a closed optimizer is an error of the caller."""
+        self.synchronize()
+        for h in self._hook_handles:
+            h.remove()
+        self._hook_handles = []
 
     def __del__(self):
         # transfers in flight still touch the pinned state and the staging buffer:

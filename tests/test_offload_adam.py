@@ -419,3 +419,28 @@ def test_qwen3_shape_builds_and_trains_a_step():
         opt.step()
         losses.append(loss.item())
     assert losses[-1] < losses[0]
+
+
+def test_close_removes_the_hooks():
+    m = make_net("cpu")
+    opt = OffloadAdam(m, lr=1e-2, mode="fp32_master", inplace_param_threshold=100)
+    x = batches(1, "cpu")[0]
+    opt.ready_for_optimizer_step = True
+    m(x).float().pow(2).mean().backward()
+    assert all(p.grad is None for p in m.parameters())  # consumed by the hooks
+    opt.step()
+    before = [p.detach().clone() for p in m.parameters()]
+    opt.close()
+    m(x).float().pow(2).mean().backward()
+    assert all(p.grad is not None for p in m.parameters())  # plain autograd again
+    assert all(torch.equal(a, b) for a, b in zip(before, m.parameters()))
+    assert opt.state_dict()["state"]  # still readable
+    # a second optimizer can take over the same model
+    for p in m.parameters():
+        p.grad = None
+    opt2 = OffloadAdam(m, lr=1e-2, mode="fp32_master", inplace_param_threshold=100)
+    opt2.ready_for_optimizer_step = True
+    m(x).float().pow(2).mean().backward()
+    opt2.step()
+    opt2.synchronize()
+    assert any(not torch.equal(a, b) for a, b in zip(before, m.parameters()))
