@@ -445,6 +445,7 @@ def main():
                 "staging_gib": (getattr(getattr(opt, "_engine", None), "staging_bytes", 0) or 0) / 2**30,
             },
             "exposed_opt_ms": exposed_ms, "peak_gpu_gb": peak_gb, "build_s": t_build,
+            "optimizer_memory_bytes": opt.memory_report() if hasattr(opt, "memory_report") else None,
             "wall_ms_per_step": wall_ms / args.steps,
             "drain_ms_after_region": drain_ms_all,
             "timing": "CUDA events on the launching stream, barrier + synchronize on both sides; the "

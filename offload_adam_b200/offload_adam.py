@@ -749,6 +749,27 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         self._finish_step()
         self._engine.synchronize()
 
+    def memory_report(self):
+        """Bytes this optimizer holds, by place: ``pinned_host`` (state of the offloaded
+        parameters, and their gradient buffers under host residency), ``device_state``
+        (state of the small parameters kept on the GPU), ``device_staging`` (the staging
+        buffer of the staged transfer) and ``device_grad_accumulators`` (bf16 gradient
+        accumulators alive right now under device residency)."""
+        def nbytes(t):
+            return t.numel() * t.element_size()
+
+        pinned = device_state = 0
+        for p in self._all_params:
+            for v in self.state[p].values():
+                if isinstance(v, torch.Tensor) and v.dim() > 0:
+                    if p in self._inplace_params:
+                        device_state += nbytes(v)
+                    else:
+                        pinned += nbytes(v)
+        return {"pinned_host": pinned, "device_state": device_state,
+                "device_staging": int(self._engine.staging_bytes),
+                "device_grad_accumulators": sum(nbytes(g) for g in self._dev_grad.values())}
+
     def close(self):
         """Detach from the model: finish everything in flight and remove the hooks, so
         that gradients reach ``p.grad`` again (for instance before building another

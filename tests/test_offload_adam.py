@@ -444,3 +444,15 @@ def test_close_removes_the_hooks():
     opt2.step()
     opt2.synchronize()
     assert any(not torch.equal(a, b) for a, b in zip(before, m.parameters()))
+
+
+def test_memory_report_counts_by_place():
+    m = torch.nn.Sequential(torch.nn.Linear(64, 64), torch.nn.Linear(64, 8)).to(torch.bfloat16)
+    opt = OffloadAdam(m, mode="fp32_master", inplace_param_threshold=600)
+    rep = opt.memory_report()
+    assert rep["pinned_host"] == 4096 * (2 + 2 + 2 + 4)          # grad, exp_avg, exp_avg_sq, master
+    assert rep["device_state"] == (64 + 512 + 8) * (2 + 2 + 2 + 4)
+    assert rep["device_staging"] == 0 and rep["device_grad_accumulators"] == 0
+    dev = OffloadAdam(torch.nn.Sequential(torch.nn.Linear(64, 64)).to(torch.bfloat16), mode="fp31_master",
+                      inplace_param_threshold=600, grad_residency="device")
+    assert dev.memory_report()["pinned_host"] == 4096 * (2 + 2 + 2)  # no host gradient buffer
