@@ -456,3 +456,21 @@ def test_memory_report_counts_by_place():
     dev = OffloadAdam(torch.nn.Sequential(torch.nn.Linear(64, 64)).to(torch.bfloat16), mode="fp31_master",
                       inplace_param_threshold=600, grad_residency="device")
     assert dev.memory_report()["pinned_host"] == 4096 * (2 + 2 + 2)  # no host gradient buffer
+
+
+@pytest.mark.parametrize("clip", [None, 1.0])
+def test_lr_scheduler_drives_the_step(clip):
+    import warnings
+    m = make_net("cpu")
+    opt = OffloadAdam(m, lr=1e-2, mode="fp32_master", max_grad_norm=clip, inplace_param_threshold=100)
+    sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda s: 0.5 ** s)
+    x = batches(1, "cpu")[0]
+    with warnings.catch_warnings(record=True) as caught:
+        warnings.simplefilter("always")
+        for _ in range(3):
+            opt.ready_for_optimizer_step = True
+            m(x).float().pow(2).mean().backward()
+            opt.step()
+            sched.step()
+    assert not [w for w in caught if "lr_scheduler" in str(w.message)]
+    assert abs(opt.param_groups[0]["lr"] - 1e-2 * 0.125) < 1e-12
