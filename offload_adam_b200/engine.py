@@ -81,7 +81,16 @@ class TransferEngine:
                     nbytes = max(int(ring_slots) * chunk_elems * 10, int(staging_bytes)) + floor
                     self.chunk_elems = chunk_elems
                     nbytes = (nbytes + 255) // 256 * 256
-                    ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+                    smallest = (max(int(ring_slots) * chunk_elems * 10, floor) + 255) // 256 * 256
+                    while True:
+                        # the buffer only buys overlap: when memory is short, take less
+                        try:
+                            ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+                            break
+                        except torch.cuda.OutOfMemoryError:
+                            if nbytes <= smallest:
+                                raise
+                            nbytes = max(smallest, nbytes // 2 // 256 * 256)
                     self.staging_bytes = nbytes
                     self._native = self.C.OffloadEngine(
                         self.device.index or 0, self.opt_stream.cuda_stream,
