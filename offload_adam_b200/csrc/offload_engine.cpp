@@ -9,6 +9,10 @@
 namespace oab {
 
 namespace {
+// Host-side waits on the helper threads are bounded as well: a wait that sees no progress
+// for this long reports an error instead of hanging the training process.
+constexpr auto kHostWaitLimit = std::chrono::seconds(300);
+
 size_t elem_extra_bytes(int mode) {
   return mode == kModeFP32Master ? 4 : (mode == kModeSR ? 0 : 2);
 }
@@ -175,7 +179,13 @@ void OffloadEngine::writer_loop() {
 void OffloadEngine::drain_writer() {
   if (!writer_.joinable()) return;
   std::unique_lock<std::mutex> lk(wb_mu_);
-  wb_idle_cv_.wait(lk, [&] { return wb_q_.empty() && !wb_busy_; });
+  // progress is one issued job; the limit applies to the time without any
+  size_t seen = wb_q_.size();
+  while (!(wb_q_.empty() && !wb_busy_)) {
+    if (!wb_idle_cv_.wait_for(lk, kHostWaitLimit, [&] { return (wb_q_.empty() && !wb_busy_) || wb_q_.size() != seen; }))
+      throw std::runtime_error("OffloadEngine: the write-back thread made no progress for 300 s");
+    seen = wb_q_.size();
+  }
   if (!wb_error_.empty()) throw std::runtime_error("OffloadEngine: write-back failed: " + wb_error_);
 }
 
@@ -211,8 +221,12 @@ OffloadEngine::Entry* OffloadEngine::allocate(size_t bytes, bool may_discard) {
       if (!overlaps(e)) break;
       if (e.queued) {
         // its write-back is with the helper thread: it will be issued, wait for that
-        while (!e.retired.load(std::memory_order_acquire))
+        const auto deadline = std::chrono::steady_clock::now() + kHostWaitLimit;
+        while (!e.retired.load(std::memory_order_acquire)) {
           std::this_thread::sleep_for(std::chrono::microseconds(20));  // chunks take milliseconds
+          if (std::chrono::steady_clock::now() > deadline)
+            throw std::runtime_error("OffloadEngine: the write-back thread made no progress for 300 s");
+        }
       }
       if (!e.retired.load(std::memory_order_acquire)) { blocked = true; break; }
     }
@@ -247,8 +261,12 @@ void OffloadEngine::wait_host_copy(const StagedStepArgs& a) {
   // the host copy must be complete: the previous write-back of this tensor
   if (a.pid >= 0 && a.pid < (int)host_ready_.size() && host_ready_set_[a.pid]) {
     // the event must have been recorded by the helper thread before it can be waited for
-    while (wb_issued_[a.pid].load(std::memory_order_acquire) < wb_submitted_[a.pid])
+    const auto deadline = std::chrono::steady_clock::now() + kHostWaitLimit;
+    while (wb_issued_[a.pid].load(std::memory_order_acquire) < wb_submitted_[a.pid]) {
       std::this_thread::sleep_for(std::chrono::microseconds(20));
+      if (std::chrono::steady_clock::now() > deadline)
+        throw std::runtime_error("OffloadEngine: the write-back thread made no progress for 300 s");
+    }
     check(cudaStreamWaitEvent(h2d_, host_ready_[a.pid], 0), "wait host_ready");
   }
   if (a.host_grad && a.pid >= 0 && a.pid < (int)grad_ready_.size() && grad_ready_set_[a.pid])
@@ -308,7 +326,8 @@ void OffloadEngine::stop_prefetch() {
     std::unique_lock<std::mutex> lk(pf_mu_);
     pf_has_plan_ = false;
     pf_plan_.clear();
-    pf_idle_cv_.wait(lk, [&] { return !pf_running_; });
+    if (!pf_idle_cv_.wait_for(lk, kHostWaitLimit, [&] { return !pf_running_; }))
+      throw std::runtime_error("OffloadEngine: the prefetch thread did not stop within 300 s");
     err.swap(pf_error_);
   }
   pf_stop_.store(false);
