@@ -33,6 +33,7 @@ How this implementation differs underneath:
 
 from __future__ import annotations
 
+import os
 import random
 import warnings
 
@@ -239,6 +240,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             # stream takes about a thousand pending operations before enqueueing blocks
             chunk_elems = 8 << 20
         self._nvtx = bool(nvtx) and self._cuda
+        self._owner_pid = os.getpid()
         self.prefetch_inflight = int(prefetch_inflight)
         if prefetch_pacing not in ("thread", "hooks"):
             raise ValueError(f"prefetch_pacing must be 'thread' or 'hooks', got {prefetch_pacing!r}")
@@ -784,7 +786,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         # transfers in flight still touch the pinned state and the staging buffer:
         # finish them before either is released
         eng = getattr(self, "_engine", None)
-        if eng is not None:
+        if eng is not None and getattr(self, "_owner_pid", None) == os.getpid():  # not in a forked child
             try:
                 eng.synchronize()
             except Exception:
