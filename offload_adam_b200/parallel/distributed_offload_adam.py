@@ -418,3 +418,74 @@ class DistributedOffloadAdam(OffloadAdam):
         super().synchronize()
         if self._symm is not None:
             self._symm.check_status(blocking=True)
+
+    # ------------------------------------------------- checkpoints across world sizes
+    def _gather_rows_to(self, shard, dst):
+        """Rows of all ranks stacked in rank order, on rank ``dst`` (None elsewhere)."""
+        world = self._world_size
+        if world <= 1:
+            return shard.detach().clone()
+        if dist.get_backend(self._pg) == "gloo" or not self._cuda:
+            parts = [torch.empty_like(shard, device="cpu") for _ in range(world)] if self._rank == dst else None
+            dist.gather(shard.detach().cpu().contiguous(), parts, dst=dist.get_global_rank(self._pg, dst),
+                        group=self._pg)
+            return torch.cat(parts, dim=0) if self._rank == dst else None
+        dev = shard.detach().to(self.device).contiguous()
+        full = torch.empty((world * dev.shape[0], *dev.shape[1:]), dtype=dev.dtype, device=self.device)
+        dist.all_gather_into_tensor(full.view(-1), dev.view(-1), group=self._pg)
+        return full.cpu() if self._rank == dst else None
+
+    @torch.no_grad()
+    def consolidated_state_dict(self, dst=0):
+        """``state_dict()`` with every sharded state tensor replaced by the full-shape
+        tensor (the rows of all ranks), returned on rank ``dst`` of the group and ``None``
+        elsewhere.  Collective: every rank must call it.  The result loads into an
+        optimizer of any world size (``load_offload_state_dict`` slices full-shape tensors
+        to the caller's rows) and into a single-GPU ``OffloadAdam``.  The reference has no
+        checkpoint logic across ranks."""
+        self.synchronize()
+        sd = super().state_dict()
+        ids = [i for g in sd["param_groups"] for i in g["params"]]
+        live = [p for g in self.param_groups for p in g["params"]]
+        out_state = {}
+        for idx, p in zip(ids, live):
+            src = sd["state"].get(idx)
+            if src is None:
+                continue
+            entry = {}
+            for k, v in src.items():
+                if isinstance(v, torch.Tensor) and k == "grad":
+                    continue  # transient accumulator, never part of a resume
+                if isinstance(v, torch.Tensor) and p in self._sharded and k in self._non_grad_keys:
+                    v = self._gather_rows_to(v, dst)
+                elif isinstance(v, torch.Tensor):
+                    v = v.detach().cpu().clone()
+                entry[k] = v
+            out_state[idx] = entry
+        if self._rank != dst:
+            return None
+        return {"state": out_state, "param_groups": sd["param_groups"]}
+
+    @torch.no_grad()
+    def load_offload_state_dict(self, state_dict):
+        """As in :class:`OffloadAdam`; state tensors of sharded parameters may also come
+        in full shape (``consolidated_state_dict()`` output, or the ``state_dict()`` of a
+        single-GPU optimizer): this rank's rows are taken."""
+        ids = [i for g in state_dict["param_groups"] for i in g["params"]]
+        live = [p for g in self.param_groups for p in g["params"]]
+        if len(ids) == len(live):
+            state = dict(state_dict["state"])
+            for idx, p in zip(ids, live):
+                src = state.get(idx)
+                if src is None or p not in self._sharded:
+                    continue
+                lo, hi = self._rows(p)
+                sliced = {}
+                for k, v in src.items():
+                    if (isinstance(v, torch.Tensor) and k in self._non_grad_keys
+                            and tuple(v.shape) == tuple(p.shape) and hi - lo != p.shape[0]):
+                        v = v[lo:hi]
+                    sliced[k] = v
+                state[idx] = sliced
+            state_dict = {"state": state, "param_groups": state_dict["param_groups"]}
+        return super().load_offload_state_dict(state_dict)

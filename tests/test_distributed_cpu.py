@@ -426,3 +426,73 @@ def test_shard_gradient_layout_rejects_the_symmetric_path():
             DistributedOffloadAdam(make_net(), grad_layout="rows")
     finally:
         dist.destroy_process_group()
+
+
+# ----------------------------------------------- checkpoints that move between world sizes
+def _reshard_worker(rank, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        kw = dict(lr=1e-2, weight_decay=0.05, mode="fp32_master", max_grad_norm=0.05,
+                  decoupled_weight_decay=True, inplace_param_threshold=200)
+        model = make_net()
+        opt = DistributedOffloadAdam(model, **kw)
+        data = rank_batches(rank, 6)
+
+        def step(m, o, b):
+            o.ready_for_optimizer_step = True
+            m(b).float().pow(2).mean().backward()
+            o.step()
+
+        step(model, opt, data[0])
+        step(model, opt, data[1])
+        full = opt.consolidated_state_dict(dst=0)
+        assert (full is None) == (rank != 0)
+        # hand the consolidated checkpoint (and the parameters) to every rank, as a file would
+        box = [full, {n: p.detach().clone() for n, p in model.named_parameters()}]
+        dist.broadcast_object_list(box, src=0)
+        full, params = box
+        a_idx = [i for i, (n, _) in enumerate(model.named_parameters()) if n == "a.weight"][0]
+        assert tuple(full["state"][a_idx]["exp_avg"].shape) == (64, 32)        # full shape again
+        assert tuple(full["state"][a_idx]["master_params"].shape) == (64, 32)
+        assert "grad" not in full["state"][a_idx]
+        # a fresh sharded optimizer resumes from the full-shape checkpoint ...
+        model2 = make_net()
+        with torch.no_grad():
+            for n, p in model2.named_parameters():
+                p.copy_(params[n])
+        opt2 = DistributedOffloadAdam(model2, **kw)
+        opt2.load_offload_state_dict(full)
+        # ... and continues exactly like the optimizer that never stopped
+        step(model, opt, data[2])
+        step(model2, opt2, data[2])
+        opt.synchronize()
+        opt2.synchronize()
+        same = all(torch.equal(p, q) for p, q in zip(model.parameters(), model2.parameters()))
+        same_state = all(torch.equal(opt.state[p][k], opt2.state[q][k])
+                         for p, q in zip(model.parameters(), model2.parameters())
+                         for k in ("exp_avg", "exp_avg_sq", "master_params"))
+        torch.save({"same": same, "same_state": same_state}, os.path.join(out_dir, f"rank{rank}.pt"))
+        if rank == 0:
+            torch.save(full, os.path.join(out_dir, "consolidated.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_consolidated_checkpoint_resumes_a_sharded_optimizer():
+    from offload_adam_b200 import OffloadAdam
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_reshard_worker, args=(free_port(), d), nprocs=WORLD, join=True)
+        reps = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(WORLD)]
+        full = torch.load(os.path.join(d, "consolidated.pt"))
+    assert all(r["same"] and r["same_state"] for r in reps), reps
+    # the same file resumes a single-process optimizer (world size 2 -> 1)
+    model = make_net()
+    single = OffloadAdam(model, lr=1e-2, weight_decay=0.05, mode="fp32_master", max_grad_norm=0.05,
+                         decoupled_weight_decay=True, inplace_param_threshold=200)
+    single.load_offload_state_dict(full)
+    a = model.a.weight
+    idx = [i for i, (n, _) in enumerate(model.named_parameters()) if n == "a.weight"][0]
+    assert single.state[a]["step"] == 2
+    assert torch.equal(single.state[a]["master_params"], full["state"][idx]["master_params"])
