@@ -474,3 +474,40 @@ def test_lr_scheduler_drives_the_step(clip):
             sched.step()
     assert not [w for w in caught if "lr_scheduler" in str(w.message)]
     assert abs(opt.param_groups[0]["lr"] - 1e-2 * 0.125) < 1e-12
+
+
+def test_state_moves_between_adam_and_offload_adam():
+    """A checkpoint of the on-GPU ``Adam`` resumes an ``OffloadAdam`` and the other way
+    round; both continue bit for bit like the optimizer that never stopped."""
+    import copy
+    kw = dict(lr=1e-2, weight_decay=0.05, mode="fp32_master", decoupled_weight_decay=True)
+    data = batches(4, "cpu")
+    m1, m2, m3 = make_net("cpu"), make_net("cpu"), make_net("cpu")
+    ref = Adam(m1.parameters(), **kw)
+
+    def ref_step(model, opt, batch):
+        for p, g in zip(model.parameters(), accumulate_in_bf16(model, [batch], 1)):
+            p.grad = g
+        opt.step()
+
+    ref_step(m1, ref, data[0])
+    ref_step(m1, ref, data[1])
+    with torch.no_grad():
+        for p, q in zip(m1.parameters(), m2.parameters()):
+            q.copy_(p)
+    off = OffloadAdam(m2, inplace_param_threshold=100, **kw)
+    off.load_offload_state_dict(copy.deepcopy(ref.state_dict()))
+    ref_step(m1, ref, data[2])
+    off.ready_for_optimizer_step = True
+    m2(data[2]).float().pow(2).mean().backward()
+    off.step()
+    off.synchronize()
+    assert all(torch.equal(p, q) for p, q in zip(m1.parameters(), m2.parameters()))
+    with torch.no_grad():
+        for p, q in zip(m2.parameters(), m3.parameters()):
+            q.copy_(p)
+    back = Adam(m3.parameters(), **kw)
+    back.load_state_dict(copy.deepcopy(off.state_dict()))
+    ref_step(m1, ref, data[3])
+    ref_step(m3, back, data[3])
+    assert all(torch.equal(p, q) for p, q in zip(m1.parameters(), m3.parameters()))
