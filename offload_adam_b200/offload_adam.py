@@ -272,6 +272,15 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         self._numa_precheck(self._offload_params, numa_node)
         self._alloc_pinned_states(self._offload_params, numa_node)
         self._alloc_inplace_states(self._inplace_params)
+        self._constructed = True
+
+    def add_param_group(self, param_group):
+        if getattr(self, "_constructed", False):
+            raise NotImplementedError(
+                f"{type(self).__name__} partitions, hooks and allocates pinned state for its "
+                "parameters at construction; build a new optimizer for a changed parameter set "
+                "(close() this one first)")
+        return super().add_param_group(param_group)
 
     # ------------------------------------------------------------------ setup
     def _register_hooks(self, model, modules, params):

@@ -511,3 +511,11 @@ def test_state_moves_between_adam_and_offload_adam():
     ref_step(m1, ref, data[3])
     ref_step(m3, back, data[3])
     assert all(torch.equal(p, q) for p, q in zip(m1.parameters(), m3.parameters()))
+
+
+def test_add_param_group_after_construction_is_refused():
+    m = make_net("cpu")
+    opt = OffloadAdam(m, mode="fp32_master", inplace_param_threshold=100)
+    extra = torch.nn.Parameter(torch.zeros(4, 4, dtype=torch.bfloat16))
+    with pytest.raises(NotImplementedError, match="construction"):
+        opt.add_param_group({"params": [extra]})
