@@ -217,6 +217,15 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         self._param2group = {p: g for g in self.param_groups for p in g["params"]}
         self.device = params[0].device if params else torch.device("cpu")
         self._cuda = self.device.type == "cuda"
+        elsewhere = {str(p.device) for p in params if p.device != self.device}
+        if elsewhere:
+            raise ValueError(
+                f"{type(self).__name__} drives one device: parameters live on {self.device} and also on "
+                f"{sorted(elsewhere)}; use one process per GPU (DistributedOffloadAdam) instead")
+        not_bf16 = {str(p.dtype) for p in params if p.dtype != _BF16 and p not in self._quant_params}
+        if not_bf16:
+            raise ValueError(f"{type(self).__name__} expects bfloat16 parameters (found {sorted(not_bf16)}); "
+                             "call model.to(torch.bfloat16) first")
 
         # first owner module in forward order; 'lazy' triggers early work only there
         self._prefetch_module = {}

@@ -519,3 +519,12 @@ def test_add_param_group_after_construction_is_refused():
     extra = torch.nn.Parameter(torch.zeros(4, 4, dtype=torch.bfloat16))
     with pytest.raises(NotImplementedError, match="construction"):
         opt.add_param_group({"params": [extra]})
+
+
+def test_construction_rejects_mixed_devices_and_non_bf16_parameters():
+    with pytest.raises(ValueError, match="bfloat16"):
+        OffloadAdam(torch.nn.Linear(8, 8), mode="fp32_master")
+    mixed = torch.nn.Sequential(torch.nn.Linear(8, 8).to(torch.bfloat16),
+                                torch.nn.Linear(8, 8, device="meta", dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="one device"):
+        OffloadAdam(mixed, mode="fp32_master")
