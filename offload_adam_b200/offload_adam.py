@@ -50,15 +50,13 @@ _BF16 = torch.bfloat16
 
 
 def get_leaf_modules_with_params(module):
-    """Leaf modules (no children) that directly own a trainable parameter, in
-    registration (= forward definition) order."""
-    out = []
-    for child in module.children():
-        if any(True for _ in child.children()):
-            out.extend(get_leaf_modules_with_params(child))
-        elif any(p.requires_grad for p in child.parameters(recurse=False)):
-            out.append(child)
-    return out
+    """Modules that directly own a trainable parameter, in registration (= forward
+    definition) order.  The reference walks the children and keeps the leaves
+    (reference: src/offload_adam/offload_adam.py:26-36), which silently leaves out
+    parameters held by a module that also has children, and every parameter of a model
+    that is itself a leaf; both are included here."""
+    return [m for m in module.modules()
+            if any(p.requires_grad for p in m.parameters(recurse=False))]
 
 
 def _offload_layout(extra_name=None, extra_dtype=None):
@@ -178,7 +176,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         modules = get_leaf_modules_with_params(model)
         params, owners = [], {}
         for m in modules:
-            for p in m.parameters():
+            for p in m.parameters(recurse=False):
                 if not p.requires_grad:
                     continue
                 if id(p) not in owners:
@@ -230,7 +228,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         # first owner module in forward order; 'lazy' triggers early work only there
         self._prefetch_module = {}
         for m in modules:
-            for p in m.parameters():
+            for p in m.parameters(recurse=False):
                 if p.requires_grad and p not in self._inplace_params:
                     self._prefetch_module.setdefault(p, m)
 
@@ -312,7 +310,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         # pacing points for the early H2D during forward (plain forward hooks add no
         # autograd nodes); not needed when the helper thread paces
         for m in (modules if self.prefetch_pacing == "hooks" else ()):
-            if any(p.requires_grad and p not in self._inplace_params for p in m.parameters()):
+            if any(p.requires_grad and p not in self._inplace_params for p in m.parameters(recurse=False)):
                 self._hook_handles.append(m.register_forward_pre_hook(lambda *_: self._pace_prefetch(1)))
 
     def _grad_accumulator_bytes(self):

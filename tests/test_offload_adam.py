@@ -523,8 +523,35 @@ def test_add_param_group_after_construction_is_refused():
 
 def test_construction_rejects_mixed_devices_and_non_bf16_parameters():
     with pytest.raises(ValueError, match="bfloat16"):
-        OffloadAdam(torch.nn.Linear(8, 8), mode="fp32_master")
+        OffloadAdam(torch.nn.Sequential(torch.nn.Linear(8, 8)), mode="fp32_master")
     mixed = torch.nn.Sequential(torch.nn.Linear(8, 8).to(torch.bfloat16),
                                 torch.nn.Linear(8, 8, device="meta", dtype=torch.bfloat16))
     with pytest.raises(ValueError, match="one device"):
         OffloadAdam(mixed, mode="fp32_master")
+
+
+class OwnsDirectly(torch.nn.Module):
+    """A module with children AND a parameter of its own."""
+
+    def __init__(self):
+        super().__init__()
+        self.scale = torch.nn.Parameter(torch.ones(32, dtype=torch.float32))
+        self.inner = torch.nn.Linear(32, 32)
+
+    def forward(self, x):
+        return self.inner(x * self.scale)
+
+
+def test_parameters_of_non_leaf_modules_and_leaf_models_are_optimized():
+    m = OwnsDirectly().to(torch.bfloat16)
+    opt = OffloadAdam(m, lr=1e-2, mode="fp32_master", inplace_param_threshold=100)
+    assert m.scale in opt.state and m.inner.weight in opt.state and len(opt._all_params) == 3
+    before = m.scale.detach().clone()
+    opt.ready_for_optimizer_step = True
+    m(torch.randn(4, 32).to(torch.bfloat16)).float().pow(2).mean().backward()
+    opt.step()
+    opt.synchronize()
+    assert not torch.equal(before, m.scale)
+    leaf = torch.nn.Linear(16, 16).to(torch.bfloat16)  # the model itself is a leaf
+    opt2 = OffloadAdam(leaf, mode="fp32_master", inplace_param_threshold=100)
+    assert len(opt2._all_params) == 2
