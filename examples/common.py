@@ -4,7 +4,6 @@ timed training loop and the JSON summary (reference: examples/e2e_train/train.py
 from __future__ import annotations
 
 import json
-import os
 import sys
 import time
 from pathlib import Path

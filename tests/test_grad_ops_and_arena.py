@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from offload_adam_b200 import _ext
-from offload_adam_b200.ops import grad_ops, oracle
+from offload_adam_b200.ops import grad_ops
 from offload_adam_b200.utils import pinned_alloc
 
 
