@@ -194,3 +194,53 @@ def test_one_adam_step_of_the_reference_kernels_agrees(tmp_path):
     if run.returncode != 0 and ("active drivers" in run.stderr or "No module named 'triton'" in run.stderr):
         pytest.skip("Triton's interpreter is not usable here")
     assert run.returncode == 0 and "OK" in run.stdout, run.stderr[-3000:]
+
+
+class TwoLinears(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.l1 = torch.nn.Linear(256, 256, bias=False)
+        self.l2 = torch.nn.Linear(256, 128, bias=True)
+        self.lm_head = torch.nn.Linear(128, 64, bias=False)
+
+    def forward(self, x):
+        return self.lm_head(self.l2(torch.relu(self.l1(x))))
+
+
+@pytest.mark.parametrize("name,kw", FORMATS)
+def test_model_state_dicts_are_interchangeable(ref_qweight, name, kw):
+    """``quantize_linears`` + ``model.state_dict()``: same keys, same bits, and each
+    package loads the other's state dict into its own quantized model."""
+    import offload_adam_b200.qweight as oq
+    kw = {k: v for k, v in kw.items() if k in ("group_size", "blocksize")}
+
+    def fresh():
+        torch.manual_seed(3)
+        return TwoLinears().to(torch.bfloat16)
+
+    theirs, ours = fresh(), fresh()
+    ref_qweight.quantize_linears(theirs, getattr(ref_qweight, name), skip_patterns=("lm_head",), **kw)
+    oq.quantize_linears(ours, getattr(oq, name), skip_patterns=("lm_head",), **kw)
+    ts, os_ = theirs.state_dict(), ours.state_dict()
+    assert list(ts) == list(os_)
+    for k in ts:
+        assert type(ts[k]) is torch.Tensor and type(os_[k]) is torch.Tensor, k
+        assert ts[k].dtype == os_[k].dtype and ts[k].shape == os_[k].shape, k
+        assert torch.equal(bits(ts[k]), bits(os_[k])), k
+    # cross-loading: a differently initialised quantized model takes the other package's file
+    torch.manual_seed(11)
+    other_ours = TwoLinears().to(torch.bfloat16)
+    oq.quantize_linears(other_ours, getattr(oq, name), skip_patterns=("lm_head",), **kw)
+    other_ours.load_state_dict(ts)
+    torch.manual_seed(12)
+    other_theirs = TwoLinears().to(torch.bfloat16)
+    ref_qweight.quantize_linears(other_theirs, getattr(ref_qweight, name), skip_patterns=("lm_head",), **kw)
+    other_theirs.load_state_dict(os_)
+    a, b = other_ours.state_dict(), other_theirs.state_dict()
+    reload_theirs = fresh()
+    ref_qweight.quantize_linears(reload_theirs, getattr(ref_qweight, name), skip_patterns=("lm_head",), **kw)
+    reload_theirs.load_state_dict(ts)
+    want = reload_theirs.state_dict()  # what the reference has after reading its own file
+    for k in want:
+        assert torch.equal(bits(a[k]), bits(want[k])), k
+        assert torch.equal(bits(b[k]), bits(want[k])), k
