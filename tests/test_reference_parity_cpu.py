@@ -51,9 +51,12 @@ def weights(shape, seed):
 
 @pytest.mark.parametrize("name,kw", FORMATS)
 @pytest.mark.parametrize("shape", [(64, 256), (40, 256), (128, 384)])
-def test_checkpoint_tensors_are_bit_identical(ref_qweight, name, kw, shape):
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_checkpoint_tensors_are_bit_identical(ref_qweight, name, kw, shape, dtype):
     import offload_adam_b200.qweight as oq
     x = weights(shape, seed=shape[0])
+    if dtype is torch.float32:  # what an fp32 master looks like: not representable in bf16
+        x = x.float() * (1.0 + 1e-3 * torch.sin(torch.arange(x.numel()).float()).reshape(x.shape))
     theirs = getattr(ref_qweight, name).from_float(x, **kw)
     ours = getattr(oq, name).from_float(x, **kw)
     tp, op = theirs.to_plain_state_dict(), ours.to_plain_state_dict()
