@@ -16,11 +16,19 @@ micro-batches).  Rank 0 prints one JSON line.
 
 Timing: W untimed warm-up steps, then exactly K steps between a barrier +
 ``torch.cuda.synchronize()`` on both sides, measured with CUDA events on the main
-stream, max over ranks.  The working set (16 GB of parameters plus activations) is far
-larger than L2, so no explicit L2 flush is needed between iterations.  ``value`` is the
-device-timed number with inputs already on the GPU; ``e2e`` repeats the measurement
-through the public API with every micro-batch's token ids copied from pinned host
-memory and the step's loss read back to the host.
+stream, max over ranks.  The closing event is recorded after every stream of the
+process has drained, so the write-back of the last step's optimizer state to the host
+is inside the timed region (in a longer run it overlaps the next forward pass).  The
+working set (16 GB of parameters plus activations) is far larger than L2, so no explicit
+L2 flush is needed between iterations.  ``value`` is the device-timed number with inputs
+already on the GPU; ``e2e`` repeats the measurement through the public API with every
+micro-batch's token ids copied from pinned host memory and the step's loss read back to
+the host.
+
+``--model-impl hf`` trains the same HuggingFace ``LlamaForCausalLM`` the reference arm
+uses (full fp32 logits) with this package's optimizer instead of the package's own
+Llama (chunked linear cross-entropy): the pair of runs separates the optimizer's share
+of a speed-up from the model code's.
 """
 
 from __future__ import annotations
@@ -58,6 +66,9 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--preset", choices=list(PRESETS), default="zero1")
     ap.add_argument("--model", choices=["llama3-8b", "llama3-70b", "tiny"], default="llama3-8b")
+    ap.add_argument("--model-impl", choices=["own", "hf"], default="own",
+                    help="this framework's arm: the package's Llama, or the HuggingFace module the reference arm trains")
+    ap.add_argument("--no-resident", action="store_true", help="stream all optimizer state every step")
     ap.add_argument("--layers", type=int, default=None, help="debug only: override layer count")
     ap.add_argument("--seq", type=int, default=None)
     ap.add_argument("--ga", type=int, default=None)
@@ -178,10 +189,13 @@ def build_ours(args, preset, device):
     from offload_adam_b200 import DistributedOffloadAdam, OffloadAdam
     from offload_adam_b200.models.llama import build_llama
     cfg = model_dims(args)
-    model = build_llama(cfg, device=device, dtype=torch.bfloat16, seed=0)
-    model.train()
-    if args.grad_ckpt:
-        model.gradient_checkpointing_enable()
+    if args.model_impl == "hf":
+        model, _ = build_hf_llama(args, preset, device)
+    else:
+        model = build_llama(cfg, device=device, dtype=torch.bfloat16, seed=0)
+        model.train()
+        if args.grad_ckpt:
+            model.gradient_checkpointing_enable()
     if args.quant != "none":
         from offload_adam_b200 import qweight
         cls = {"nvfp4": qweight.NVFP4QWeight, "nf4": qweight.NF4QWeight, "int4": qweight.Int4QWeight,
@@ -199,20 +213,25 @@ def build_ours(args, preset, device):
         common["async_writeback"] = False
     if args.prefetch_inflight is not None:
         common["prefetch_inflight"] = args.prefetch_inflight
+    if args.no_resident:
+        common["keep_resident"] = False
     if preset["optimizer"] == "distributed":
         opt = DistributedOffloadAdam(model, comm=args.comm, grad_layout=args.grad_layout, **common)
     else:
         opt = OffloadAdam(model, **common)
 
-    def loss_fn(ids):
-        return model(ids, labels=ids)
+    if args.model_impl == "hf":
+        def loss_fn(ids):
+            return model(input_ids=ids, labels=ids).loss
+    else:
+        def loss_fn(ids):
+            return model(ids, labels=ids)
 
     return model, opt, loss_fn, cfg.vocab_size
 
 
-def build_reference(args, preset, device):
-    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
-    import offload_adam as ref  # the unmodified reference package
+def build_hf_llama(args, preset, device):
+    """Random-init HuggingFace LlamaForCausalLM of the benchmark's shape (bf16, SDPA)."""
     from transformers import LlamaConfig, LlamaForCausalLM
     d = model_dims(args)
     hf = LlamaConfig(vocab_size=d.vocab_size, hidden_size=d.hidden_size, intermediate_size=d.intermediate_size,
@@ -233,6 +252,13 @@ def build_reference(args, preset, device):
     model.train()
     if args.grad_ckpt:
         model.gradient_checkpointing_enable()
+    return model, d.vocab_size
+
+
+def build_reference(args, preset, device):
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    import offload_adam as ref  # the unmodified reference package
+    model, vocab = build_hf_llama(args, preset, device)
     if args.quant != "none":
         from offload_adam import qweight as rq  # the reference's own formats
         cls = {"nvfp4": rq.NVFP4QWeight, "nf4": rq.NF4QWeight, "int4": rq.Int4QWeight,
@@ -249,7 +275,7 @@ def build_reference(args, preset, device):
     def loss_fn(ids):
         return model(input_ids=ids, labels=ids).loss
 
-    return model, opt, loss_fn, d.vocab_size
+    return model, opt, loss_fn, vocab
 
 
 # ------------------------------------------------------------------------ training
@@ -309,27 +335,27 @@ def run_steps(n_steps, ga, opt, loss_fn, batches_dev=None, batches_host=None, de
 
 
 def timed(fn, device, wait_writeback=None):
-    """Returns (event ms on the launching stream, host wall ms until ``fn`` returned,
-    drain ms, fn's result).  Bracketed by barrier + synchronize on both sides.  The
-    drain is what was still running on other streams when the launching stream was
-    done: the write-back of the last step's optimizer state, which in a longer run
-    overlaps the next forward pass."""
+    """Returns (event ms, host wall ms until ``fn`` returned, drain ms, fn's result).
+    Bracketed by barrier + synchronize on both sides.  The closing event is recorded on
+    the launching stream once every stream of the process is idle, so the event time
+    includes the drain: what was still running on other streams when the launching stream
+    was done (the write-back of the last step's optimizer state, which in a longer run
+    overlaps the next forward pass).  ``drain`` reports that part on its own."""
     dist.barrier()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
     t0 = time.perf_counter()
     e0.record()
     out = fn()
     e1.record()
     wall = time.perf_counter() - t0
-    e1.synchronize()
-    t1 = time.perf_counter()
     if wait_writeback is not None:
         wait_writeback()  # also waits for write-backs a helper thread has not issued yet
     torch.cuda.synchronize()
-    drain = time.perf_counter() - t1
+    e2.record()
+    e2.synchronize()
     dist.barrier()
-    return e0.elapsed_time(e1), wall * 1e3, drain * 1e3, out
+    return e0.elapsed_time(e2), wall * 1e3, e1.elapsed_time(e2), out
 
 
 def main():
@@ -371,14 +397,20 @@ def main():
 
     sampler = ClockSampler(local_rank)
     sampler.start()
+    moved0 = None
     if args.impl == "ours":
         launches0 = C.launch_count()
+        moved0 = opt._engine.bytes_moved() if hasattr(opt, "_engine") else None
     exposed = []
     ms, wall_ms, drain_ms, _ = timed(lambda: run_steps(args.steps, ga, opt, loss_fn, batches_dev=dev_batches,
                                                        exposed=exposed), device,
                                      getattr(opt, "wait_writeback", None))
     launches = (C.launch_count() - launches0) if launches0 is not None else None
     clocks = sampler.stop()
+    link_bytes = None
+    moved1 = opt._engine.bytes_moved() if args.impl == "ours" and hasattr(opt, "_engine") else None
+    if moved0 is not None and moved1 is not None:
+        link_bytes = {"h2d": (moved1[0] - moved0[0]) / args.steps, "d2h": (moved1[1] - moved0[1]) / args.steps}
     exposed_ms = statistics.mean(a.elapsed_time(b) for a, b in exposed) if exposed else None
     ms = max_over_ranks(ms, device)
     drain_ms_all = max_over_ranks(drain_ms, device)
@@ -443,14 +475,17 @@ def main():
                 "grad_layout": getattr(opt, "grad_layout", None),
                 "quant": args.quant,
                 "staging_gib": (getattr(getattr(opt, "_engine", None), "staging_bytes", 0) or 0) / 2**30,
+                "resident_gib": (getattr(getattr(opt, "_engine", None), "resident_bytes", 0) or 0) / 2**30,
+                "model_impl": args.model_impl if args.impl == "ours" else "hf",
             },
+            "optimizer_link_bytes_per_step": link_bytes,
             "exposed_opt_ms": exposed_ms, "peak_gpu_gb": peak_gb, "build_s": t_build,
             "optimizer_memory_bytes": opt.memory_report() if hasattr(opt, "memory_report") else None,
             "wall_ms_per_step": wall_ms / args.steps,
             "drain_ms_after_region": drain_ms_all,
-            "timing": "CUDA events on the launching stream, barrier + synchronize on both sides; the "
-                      "write-back of the last step's optimizer state (drain_ms_after_region) finishes "
-                      "after the region, as it does behind the next forward pass in a longer run",
+            "timing": "CUDA events on the launching stream, barrier + synchronize on both sides; the closing "
+                      "event is recorded after all streams drained, so the write-back of the last step's "
+                      "optimizer state (drain_ms_after_region, part of the timed region) is included",
             "clocks": clocks,
             "e2e": e2e, "gpu_launches": launches,
         }

@@ -2,15 +2,18 @@
 
 The extension is compiled in-tree for sm_100a only
 (``-gencode arch=compute_100a,code=sm_100a``) and imported from the package
-directory.  ``load()`` imports a prebuilt ``_C*.so`` when one is present and
-builds it otherwise; ``build()`` always (re)builds when a source is newer than
-the binary.  On a machine with a CUDA device a missing extension is an error:
-nothing silently falls back to eager PyTorch there.
+directory.  Every build records a digest of all files under ``csrc/`` next to the
+binary; ``load()`` imports a prebuilt ``_C*.so`` only when that digest matches the
+sources it finds, and rebuilds (one process at a time, under a file lock) otherwise,
+so an edited kernel can never run from an old binary.  On a machine with a CUDA
+device a missing extension is an error: nothing silently falls back to eager
+PyTorch there.
 """
 
 from __future__ import annotations
 
 import glob
+import hashlib
 import importlib
 import importlib.util
 import os
@@ -49,12 +52,30 @@ def _so_path():
     return cands[0] if cands else None
 
 
+_DIGEST_FILE = os.path.join(_PKG_DIR, _NAME + ".digest")
+
+
+def source_digest():
+    """SHA-256 over the names and contents of every file under ``csrc/`` and the flags."""
+    h = hashlib.sha256()
+    deps = sorted(sources() + glob.glob(os.path.join(_CSRC, "*.h")) + glob.glob(os.path.join(_CSRC, "*.cuh")))
+    for path in deps:
+        h.update(os.path.basename(path).encode())
+        with open(path, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(NVCC_FLAGS + CXX_FLAGS).encode())
+    return h.hexdigest()
+
+
 def _stale(so):
+    """True when there is no binary or it was not built from the sources present now."""
     if so is None:
         return True
-    t = os.path.getmtime(so)
-    deps = sources() + glob.glob(os.path.join(_CSRC, "*.h")) + glob.glob(os.path.join(_CSRC, "*.cuh"))
-    return any(os.path.getmtime(s) > t for s in deps)
+    try:
+        with open(_DIGEST_FILE) as f:
+            return f.read().strip() != source_digest()
+    except OSError:
+        return True
 
 
 def _import_so(path):
@@ -71,12 +92,18 @@ def build(verbose=False, force=False):
     import torch  # noqa: F401  (must be imported before the extension)
     from torch.utils import cpp_extension
 
-    with _lock:
+    import fcntl
+
+    with _lock, open(os.path.join(_PKG_DIR, "." + _NAME + ".lock"), "w") as lock_file:
+        fcntl.flock(lock_file, fcntl.LOCK_EX)  # ranks of one job build one at a time; the others reuse
         so = _so_path()
         if so is not None and not force and not _stale(so):
             if _module is None:
                 _module = _import_so(so)
             return _module
+        if _module is not None:
+            raise RuntimeError("offload_adam_b200: the sources under csrc/ changed after the extension was "
+                               "imported; restart the process to rebuild")
         build_dir = os.path.join(_PKG_DIR, "build")
         os.makedirs(build_dir, exist_ok=True)
         os.environ.setdefault("MAX_JOBS", str(min(8, os.cpu_count() or 4)))
@@ -97,6 +124,8 @@ def build(verbose=False, force=False):
         import shutil
 
         shutil.copy2(built, target)
+        with open(_DIGEST_FILE, "w") as f:
+            f.write(source_digest())
         _module = _import_so(target)
         return _module
 
@@ -115,7 +144,7 @@ def load(required=None):
     if required is None:
         required = torch.cuda.is_available()
     so = _so_path()
-    if so is not None:
+    if so is not None and not _stale(so):
         try:
             with _lock:
                 if _module is None:

@@ -29,13 +29,16 @@ struct AdamStepArgs {
   void* m = nullptr;         // bf16 exp_avg (in/out)
   void* v = nullptr;         // bf16 exp_avg_sq (in/out)
   void* extra = nullptr;     // fp32 master (fp32_master) or int16 rounding error
+  void* extra_copy = nullptr;  // fp32_master only: the updated master is stored here as well
+                               // (device memory; lets a later pass re-quantize the weight
+                               // after `extra`, a staging chunk, has gone back to the host)
   int64_t n = 0;             // elements
   float lr = 0.f, wd = 0.f, beta1_hat = 0.f, beta2_hat = 0.f, eps = 0.f;
   const float* clip_coef = nullptr;  // optional device scalar multiplied into g (fp32)
   uint64_t seed = 0;                 // stochastic rounding stream
   int64_t elem_offset = 0;           // global index of element 0 (keeps SR stream
                                      // independent of how a tensor is chunked)
-  float* amax_out = nullptr;         // optional: atomic max of |updated master| (fp32 bits)
+  float* amax_out = nullptr;         // optional, fp32_master only: atomic max of |updated master| (fp32 bits)
   int max_ctas = 0;                  // 0 = size for HBM streaming; small values keep
                                      // most SMs free for concurrent GEMMs
 

@@ -5,6 +5,7 @@
 
 #include <optional>
 
+#include "adam_quant.h"
 #include "adam_step.h"
 #include "grad_ops.h"
 #include "offload_engine.h"
@@ -118,10 +119,15 @@ void adam_step(int64_t mode, const OptT& p, const OptT& g, const OptT& g2, const
                const Tensor& v, const OptT& extra, double lr, double wd, double b1h, double b2h,
                double eps, bool decoupled, const OptT& clip, int64_t seed, int64_t elem_offset,
                const OptT& amax, int64_t max_ctas, int64_t stream, const std::vector<int64_t>& g_peers,
-               double g_scale, const std::vector<int64_t>& p_peers, const OptT& status) {
+               double g_scale, const std::vector<int64_t>& p_peers, const OptT& status, const OptT& extra_copy) {
   auto a = make_args(mode, p, g, g2, m, v, extra, lr, wd, b1h, b2h, eps, decoupled, clip, seed,
                      elem_offset, amax, max_ctas);
   set_peers(a, g_peers, g_scale, p_peers, status);
+  if (extra_copy.has_value() && extra_copy->defined()) {
+    TORCH_CHECK(extra_copy->is_cuda() && extra_copy->scalar_type() == at::kFloat && extra_copy->numel() == a.n,
+                "extra_copy: CUDA fp32 of the state's size");
+    a.extra_copy = extra_copy->data_ptr();
+  }
   TORCH_CHECK(a.g != nullptr || a.n_g_peers > 0, "adam_step needs a gradient");
   cu_check(oab::launch_adam_step(a, pick_stream(stream)), "adam_step launch");
 }
@@ -194,6 +200,60 @@ void multi_tensor_adam(const Tensor& table, const Tensor& block_map, int64_t mod
 }
 
 // ---------------------------------------------------------------------------
+// Quantized weights: where the packed rows of a step go
+// ---------------------------------------------------------------------------
+struct PyQuantSpec {
+  oab::QuantPushArgs q;
+  Tensor amax_keep, gscale_keep;  // keep the scalars alive
+  PyQuantSpec(int64_t format, int64_t out_f, int64_t in_f, int64_t row0, int64_t group, int64_t scale_dtype,
+              const std::vector<int64_t>& payload0, const std::vector<int64_t>& payload1, const OptT& tensor_amax,
+              const OptT& global_scale) {
+    TORCH_CHECK(!payload0.empty() && payload0.size() <= (size_t)oab::kMaxPeers && payload1.size() == payload0.size(),
+                "1..", oab::kMaxPeers, " replicas, two payload tensors each");
+    q.format = (int)format;
+    q.out_f = out_f;
+    q.in_f = in_f;
+    q.row0 = row0;
+    q.group = (int)group;
+    q.scale_dtype = (int)scale_dtype;
+    q.n_replicas = (int)payload0.size();
+    for (size_t j = 0; j < payload0.size(); ++j) {
+      q.payload0[j] = reinterpret_cast<void*>(payload0[j]);
+      q.payload1[j] = reinterpret_cast<void*>(payload1[j]);
+    }
+    if (tensor_amax.has_value() && tensor_amax->defined()) {
+      TORCH_CHECK(tensor_amax->is_cuda() && tensor_amax->scalar_type() == at::kFloat, "tensor_amax: CUDA fp32");
+      amax_keep = *tensor_amax;
+      q.tensor_amax = amax_keep.data_ptr<float>();
+    }
+    if (global_scale.has_value() && global_scale->defined()) {
+      TORCH_CHECK(global_scale->is_cuda() && global_scale->scalar_type() == at::kFloat, "global_scale: CUDA fp32");
+      gscale_keep = *global_scale;
+      q.global_scale_out = gscale_keep.data_ptr<float>();
+    }
+  }
+};
+
+// Adam + re-quantize + push on device-resident operands (tests, micro-benchmarks; the
+// optimizers go through OffloadEngine.staged_step).
+void adam_quant_push(const PyQuantSpec& spec, const OptT& g, const OptT& g2, const Tensor& m, const Tensor& v,
+                     const Tensor& master, double lr, double wd, double b1h, double b2h, double eps, bool decoupled,
+                     const OptT& clip, int64_t max_ctas, int64_t stream, const std::vector<int64_t>& g_peers,
+                     double g_scale, const OptT& status) {
+  auto a = make_args(oab::kModeFP32Master, OptT(), g, g2, m, v, OptT(master), lr, wd, b1h, b2h, eps, decoupled,
+                     clip, 0, 0, OptT(), max_ctas);
+  set_peers(a, g_peers, g_scale, {}, status);
+  cu_check(oab::launch_adam_quant_push(a, spec.q, pick_stream(stream)), "adam_quant_push launch");
+}
+
+void nvfp4_quantize_push(const PyQuantSpec& spec, int64_t master_ptr, int64_t n, const OptT& status, int64_t stream) {
+  const int* abort_flag = (status.has_value() && status->defined()) ? reinterpret_cast<const int*>(dev_ptr(*status)) : nullptr;
+  cu_check(oab::launch_nvfp4_quantize_push(reinterpret_cast<const float*>(master_ptr), n, spec.q, abort_flag,
+                                           pick_stream(stream)),
+           "nvfp4_quantize_push launch");
+}
+
+// ---------------------------------------------------------------------------
 // Pinned arena
 // ---------------------------------------------------------------------------
 struct PyArena {
@@ -257,11 +317,12 @@ struct PyEngine {
         reinterpret_cast<cudaStream_t>(d2h), workspace.data_ptr(),
         (size_t)workspace.numel() * workspace.element_size(), o, (int)n_tensors);
   }
-  void staged_step(int64_t pid, int64_t mode, const OptT& p, const OptT& g, const OptT& host_grad,
-                   const Tensor& m, const Tensor& v, const OptT& extra, double lr, double wd, double b1h,
-                   double b2h, double eps, bool decoupled, const OptT& clip, int64_t seed,
-                   int64_t elem_offset, const OptT& amax, const std::vector<int64_t>& g_peers,
-                   double g_scale, const std::vector<int64_t>& p_peers, const OptT& status) {
+  int64_t staged_step(int64_t pid, int64_t mode, const OptT& p, const OptT& g, const OptT& host_grad,
+                      const Tensor& m, const Tensor& v, const OptT& extra, double lr, double wd, double b1h,
+                      double b2h, double eps, bool decoupled, const OptT& clip, int64_t seed,
+                      int64_t elem_offset, const OptT& amax, const std::vector<int64_t>& g_peers,
+                      double g_scale, const std::vector<int64_t>& p_peers, const OptT& status, int64_t chunk,
+                      const PyQuantSpec* quant, const OptT& master_copy) {
     TORCH_CHECK(!m.is_cuda() && !v.is_cuda(), "staged_step: state tensors must be pinned host tensors");
     oab::StagedStepArgs a;
     a.pid = (int)pid;
@@ -284,12 +345,24 @@ struct PyEngine {
     k.seed = (uint64_t)seed;
     k.elem_offset = elem_offset;
     if (amax.has_value() && amax->defined()) k.amax_out = amax->data_ptr<float>();
+    a.chunk = chunk;
+    if (quant != nullptr) a.quant = &quant->q;
+    if (master_copy.has_value() && master_copy->defined()) {
+      TORCH_CHECK(master_copy->is_cuda() && master_copy->scalar_type() == at::kFloat && master_copy->numel() >= k.n,
+                  "master_copy: CUDA fp32 of at least the tensor's size");
+      a.master_copy = master_copy->data_ptr();
+    }
+    void* where = nullptr;
     {
       // may wait for staging space (write-backs issued by the helper thread)
       py::gil_scoped_release nogil;
-      eng->staged_step(a);
+      where = eng->staged_step(a);
     }
+    return reinterpret_cast<int64_t>(where);
   }
+  bool make_resident(int64_t pid, int64_t mode, int64_t n) { return eng->make_resident((int)pid, (int)mode, n); }
+  bool is_resident(int64_t pid) const { return eng->is_resident((int)pid); }
+  int64_t resident_bytes() const { return (int64_t)eng->resident_bytes(); }
   void staged_grad_to_host(int64_t pid, const Tensor& host_grad, const Tensor& dev_grad, bool first,
                            const OptT& sumsq, const OptT& scratch) {
     TORCH_CHECK(!host_grad.is_cuda() && dev_grad.is_cuda() && host_grad.numel() == dev_grad.numel(), "grad buffers");
@@ -299,7 +372,7 @@ struct PyEngine {
   }
   std::pair<int64_t, bool> prefetch(int64_t pid, int64_t mode, const OptT& host_grad, const Tensor& m,
                                     const Tensor& v, const OptT& extra, int64_t from_off,
-                                    int64_t max_chunks, int64_t max_inflight) {
+                                    int64_t max_chunks, int64_t max_inflight, int64_t chunk) {
     TORCH_CHECK(!m.is_cuda() && !v.is_cuda(), "prefetch: state tensors must be pinned host tensors");
     oab::StagedStepArgs a;
     a.pid = (int)pid;
@@ -309,11 +382,12 @@ struct PyEngine {
     a.k.v = v.data_ptr();
     if (extra.has_value() && extra->defined()) a.k.extra = extra->data_ptr();
     if (host_grad.has_value() && host_grad->defined()) a.host_grad = host_grad->data_ptr();
+    a.chunk = chunk;
     bool full = false;
     int64_t off = eng->prefetch(a, from_off, max_chunks, (int)max_inflight, &full);
     return {off, full};
   }
-  void start_prefetch(int64_t mode, const std::vector<std::tuple<int64_t, Tensor, Tensor, OptT>>& items,
+  void start_prefetch(int64_t mode, const std::vector<std::tuple<int64_t, Tensor, Tensor, OptT, int64_t>>& items,
                       int64_t max_inflight) {
     std::vector<oab::OffloadEngine::PrefetchItem> plan;
     plan.reserve(items.size());
@@ -329,6 +403,7 @@ struct PyEngine {
       x.m = m.data_ptr();
       x.v = v.data_ptr();
       if (extra.has_value() && extra->defined()) x.extra = extra->data_ptr();
+      x.chunk = std::get<4>(it);
       plan.push_back(x);
     }
     py::gil_scoped_release nogil;
@@ -344,6 +419,7 @@ struct PyEngine {
     eng->join(s);
   }
   void join_compute(int64_t stream) { eng->join_compute(pick_stream(stream)); }
+  void wait_host_grad(int64_t pid) { eng->wait_host_grad((int)pid); }
   void discard_prefetched() { eng->discard_prefetched(); }
   int64_t prefetched_chunks() const { return eng->prefetched_chunks(); }
   int64_t prefetched_bytes() const { return eng->prefetched_bytes(); }
@@ -368,7 +444,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("clip") = py::none(), py::arg("seed") = 0, py::arg("elem_offset") = 0,
         py::arg("amax") = py::none(), py::arg("max_ctas") = 0, py::arg("stream") = 0,
         py::arg("g_peers") = std::vector<int64_t>(), py::arg("g_scale") = 1.0,
-        py::arg("p_peers") = std::vector<int64_t>(), py::arg("status") = py::none());
+        py::arg("p_peers") = std::vector<int64_t>(), py::arg("status") = py::none(),
+        py::arg("extra_copy") = py::none());
   m.def("grad_accumulate", &grad_accumulate, py::arg("out"), py::arg("a"), py::arg("b"),
         py::arg("sumsq") = py::none(), py::arg("sumsq_accumulate") = false,
         py::arg("scratch") = py::none(), py::arg("max_ctas") = 0, py::arg("stream") = 0);
@@ -396,6 +473,29 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("tensor", &PyArena::tensor)
       .def("stats", &PyArena::stats);
 
+  py::class_<PyQuantSpec>(m, "QuantSpec")
+      .def(py::init<int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, const std::vector<int64_t>&,
+                    const std::vector<int64_t>&, const OptT&, const OptT&>(),
+           py::arg("format"), py::arg("out_f"), py::arg("in_f"), py::arg("row0"), py::arg("group"),
+           py::arg("scale_dtype"), py::arg("payload0"), py::arg("payload1"), py::arg("tensor_amax") = py::none(),
+           py::arg("global_scale") = py::none());
+  m.def("adam_quant_supported", [](int64_t format, int64_t in_f, int64_t group) {
+    return oab::adam_quant_supported((int)format, in_f, (int)group);
+  });
+  m.def("adam_quant_push", &adam_quant_push, py::arg("spec"), py::arg("g"), py::arg("g2"), py::arg("m"), py::arg("v"),
+        py::arg("master"), py::arg("lr"), py::arg("wd"), py::arg("beta1_hat"), py::arg("beta2_hat"), py::arg("eps"),
+        py::arg("decoupled"), py::arg("clip") = py::none(), py::arg("max_ctas") = 0, py::arg("stream") = 0,
+        py::arg("g_peers") = std::vector<int64_t>(), py::arg("g_scale") = 1.0, py::arg("status") = py::none());
+  m.def("nvfp4_quantize_push", &nvfp4_quantize_push, py::arg("spec"), py::arg("master_ptr"), py::arg("n"),
+        py::arg("status") = py::none(), py::arg("stream") = 0);
+  m.attr("QFMT_NVFP4") = (int)oab::kQNVFP4;
+  m.attr("QFMT_NF4") = (int)oab::kQNF4;
+  m.attr("QFMT_INT4") = (int)oab::kQInt4;
+  m.attr("QFMT_INT8") = (int)oab::kQInt8;
+  m.attr("QDT_F32") = (int)oab::kF32;
+  m.attr("QDT_BF16") = (int)oab::kBF16;
+  m.attr("QDT_F16") = (int)oab::kF16;
+
   py::class_<PyEngine>(m, "OffloadEngine")
       .def(py::init<int64_t, int64_t, int64_t, int64_t, Tensor, int64_t, int64_t, int64_t, bool>())
       .def_static("min_ring_bytes", [](int64_t chunk_elems) {
@@ -406,11 +506,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("lr"), py::arg("wd"), py::arg("beta1_hat"), py::arg("beta2_hat"), py::arg("eps"),
            py::arg("decoupled"), py::arg("clip"), py::arg("seed"), py::arg("elem_offset"),
            py::arg("amax"), py::arg("g_peers") = std::vector<int64_t>(), py::arg("g_scale") = 1.0,
-           py::arg("p_peers") = std::vector<int64_t>(), py::arg("status") = py::none())
+           py::arg("p_peers") = std::vector<int64_t>(), py::arg("status") = py::none(), py::arg("chunk") = 0,
+           py::arg("quant") = nullptr, py::arg("master_copy") = py::none())
+      .def("make_resident", &PyEngine::make_resident)
+      .def("is_resident", &PyEngine::is_resident)
+      .def("resident_bytes", &PyEngine::resident_bytes)
       .def("staged_grad_to_host", &PyEngine::staged_grad_to_host)
-      .def("prefetch", &PyEngine::prefetch)
+      .def("prefetch", &PyEngine::prefetch, py::arg("pid"), py::arg("mode"), py::arg("host_grad"), py::arg("m"),
+           py::arg("v"), py::arg("extra"), py::arg("from_off"), py::arg("max_chunks"), py::arg("max_inflight"),
+           py::arg("chunk") = 0)
       .def("join", &PyEngine::join)
       .def("join_compute", &PyEngine::join_compute)
+      .def("wait_host_grad", &PyEngine::wait_host_grad)
       .def("discard_prefetched", &PyEngine::discard_prefetched)
       .def("wait_writebacks", &PyEngine::wait_writebacks)
       .def("start_prefetch", &PyEngine::start_prefetch)

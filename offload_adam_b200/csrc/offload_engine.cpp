@@ -33,7 +33,8 @@ void OffloadEngine::check(cudaError_t e, const char* what) {
 OffloadEngine::OffloadEngine(int device, cudaStream_t compute, cudaStream_t h2d, cudaStream_t d2h,
                              void* workspace, size_t ws_bytes, const EngineOptions& opt,
                              int n_tensors)
-    : device_(device), compute_(compute), h2d_(h2d), d2h_(d2h), opt_(opt) {
+    : device_(device), compute_(compute), h2d_(h2d), d2h_(d2h), opt_(opt),
+      res_(n_tensors > 0 ? (size_t)n_tensors : 0) {
   if (opt_.chunk_elems % 16 != 0 || opt_.chunk_elems <= 0)
     throw std::invalid_argument("OffloadEngine: chunk_elems must be a positive multiple of 16");
   if (ws_bytes < min_ring_bytes(opt_.chunk_elems))
@@ -192,6 +193,8 @@ void OffloadEngine::drain_writer() {
 void OffloadEngine::discard_prefetched() {
   stop_prefetch();
   discard_impl();
+  // the host copy was changed behind the engine's back: resident state is stale too
+  for (Resident& r : res_) r.loaded = false;
 }
 
 void OffloadEngine::discard_impl() {
@@ -360,6 +363,7 @@ void OffloadEngine::loader_loop() {
         a.k.m = plan[i].m;
         a.k.v = plan[i].v;
         a.k.extra = plan[i].extra;
+        a.chunk = plan[i].chunk;
         int64_t off = 0;
         while (off < a.k.n) {
           if (pf_stop_.load()) { done = true; break; }
@@ -391,10 +395,16 @@ int64_t OffloadEngine::prefetch(const StagedStepArgs& a, int64_t from_off, int64
 int64_t OffloadEngine::prefetch_impl(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks,
                                      int max_inflight, bool* full) {
   const AdamStepArgs& k = a.k;
-  const int64_t C = opt_.chunk_elems;
+  const int64_t C = chunk_of(a);
   int64_t off = from_off, issued = 0;
   bool waited = false;
   if (full) *full = false;
+  if (is_resident(a.pid)) {
+    // loaded once; afterwards there is nothing to bring in for this tensor
+    Resident& r = res_[a.pid];
+    if (!r.loaded) load_resident(a, r);
+    return k.n;
+  }
   while (off < k.n && (max_chunks <= 0 || issued < max_chunks)) {
     if (max_inflight > 0) {
       while (!inflight_.empty() && cudaEventQuery(inflight_.front()->h2d_done) == cudaSuccess)
@@ -418,12 +428,115 @@ int64_t OffloadEngine::prefetch_impl(const StagedStepArgs& a, int64_t from_off, 
   return off;
 }
 
-void OffloadEngine::staged_step(const StagedStepArgs& a) {
+cudaError_t OffloadEngine::launch_chunk(const StagedStepArgs& a, const AdamStepArgs& c, int64_t off) {
+  if (a.quant == nullptr) return launch_adam_step(c, compute_);
+  if (a.quant->format == kQNVFP4) return launch_adam_step(c, compute_);  // quantized by a later pass
+  QuantPushArgs q = *a.quant;
+  q.row0 = a.quant->row0 + off / q.in_f;
+  return launch_adam_quant_push(c, q, compute_);
+}
+
+bool OffloadEngine::make_resident(int pid, int mode, int64_t n) {
+  if (pid < 0 || pid >= (int)res_.size() || n <= 0) return false;
+  if (res_[pid].on) return true;
+  stop_prefetch();
+  if (!live_.empty() || head_ != 0)
+    throw std::runtime_error("OffloadEngine: make_resident after the staging buffer came into use");
+  const size_t xb = elem_extra_bytes(mode);
+  const size_t need = 2 * up256(2 * n) + up256(xb * n);
+  if (need + min_ring_bytes(opt_.chunk_elems) > ring_bytes_) return false;
+  Resident& r = res_[pid];
+  r.on = true;
+  r.loaded = false;
+  r.mode = mode;
+  r.n = n;
+  r.m = ring_;
+  r.v = r.m + up256(2 * n);
+  r.x = r.v + up256(2 * n);
+  r.h2d_done = take_event();
+  r.k_done = take_event();
+  r.free_ev = take_event();
+  ring_ += need;
+  ring_bytes_ -= need;
+  res_bytes_ += need;
+  return true;
+}
+
+void OffloadEngine::load_resident(const StagedStepArgs& a, Resident& r) {
+  const AdamStepArgs& k = a.k;
+  const size_t xb = elem_extra_bytes(k.mode);
+  if (k.n != r.n || k.mode != r.mode) throw std::runtime_error("OffloadEngine: resident tensor changed size or mode");
+  wait_host_copy(a);
+  check(cudaMemcpyAsync(r.m, k.m, 2 * r.n, cudaMemcpyHostToDevice, h2d_), "h2d m");
+  check(cudaMemcpyAsync(r.v, k.v, 2 * r.n, cudaMemcpyHostToDevice, h2d_), "h2d v");
+  if (xb) check(cudaMemcpyAsync(r.x, k.extra, xb * r.n, cudaMemcpyHostToDevice, h2d_), "h2d x");
+  bytes_h2d_ += (int64_t)((4 + xb) * r.n);
+  check(cudaEventRecord(r.h2d_done, h2d_), "record");
+  r.loaded = true;
+}
+
+void* OffloadEngine::step_resident(const StagedStepArgs& a, Resident& r) {
+  const AdamStepArgs& k = a.k;
+  const size_t xb = elem_extra_bytes(k.mode);
+  if (a.host_grad != nullptr)
+    throw std::runtime_error("OffloadEngine: resident tensors take their gradient from the device");
+  const bool fresh = !r.loaded;
+  if (fresh) load_resident(a, r);
+  if (k.n != r.n || k.mode != r.mode) throw std::runtime_error("OffloadEngine: resident tensor changed size or mode");
+  // the last load (first step after a (re)load) and the last write-back (it still reads
+  // the buffers this step overwrites) come first
+  check(cudaStreamWaitEvent(compute_, r.h2d_done, 0), "wait h2d");
+  if (!fresh && host_ready_set_[a.pid]) {
+    const auto deadline = std::chrono::steady_clock::now() + kHostWaitLimit;
+    while (wb_issued_[a.pid].load(std::memory_order_acquire) < wb_submitted_[a.pid]) {
+      std::this_thread::sleep_for(std::chrono::microseconds(20));
+      if (std::chrono::steady_clock::now() > deadline)
+        throw std::runtime_error("OffloadEngine: the write-back thread made no progress for 300 s");
+    }
+    check(cudaStreamWaitEvent(compute_, host_ready_[a.pid], 0), "wait write-back");
+  }
+  if (a.quant != nullptr && a.quant->format == kQNVFP4 && k.amax_out != nullptr)
+    check(cudaMemsetAsync(k.amax_out, 0, sizeof(float), compute_), "clear amax");
+  AdamStepArgs c = k;
+  if (k.n_g_peers > 0) { c.g = nullptr; c.g2 = nullptr; }
+  c.m = r.m; c.v = r.v; c.extra = xb ? r.x : nullptr;
+  c.extra_copy = nullptr;  // the resident master is the device copy
+  c.max_ctas = opt_.max_ctas;
+  check(launch_chunk(a, c, 0), "adam_step");
+  check(cudaEventRecord(r.k_done, compute_), "record");
+
+  WbJob j;
+  r.wb.retired.store(false, std::memory_order_relaxed);
+  j.e = &r.wb;
+  j.k_done = r.k_done;
+  j.free_ev = r.free_ev;
+  j.host[0] = k.m; j.dev[0] = r.m; j.bytes[0] = 2 * r.n;
+  j.host[1] = k.v; j.dev[1] = r.v; j.bytes[1] = 2 * r.n;
+  j.n = 2;
+  if (xb) { j.host[2] = k.extra; j.dev[2] = r.x; j.bytes[2] = xb * r.n; j.n = 3; }
+  bytes_d2h_ += (int64_t)((4 + xb) * r.n);
+  j.pid = a.pid;
+  submit_writeback(j);
+  return (a.quant != nullptr && a.quant->format == kQNVFP4) ? (void*)r.x : nullptr;
+}
+
+void* OffloadEngine::staged_step(const StagedStepArgs& a) {
   stop_prefetch();
   const AdamStepArgs& k = a.k;
-  const int64_t C = opt_.chunk_elems;
+  if (a.quant != nullptr) {
+    if (k.mode != kModeFP32Master) throw std::invalid_argument("OffloadEngine: quantized weights need fp32_master");
+    if (a.quant->in_f <= 0 || k.n % a.quant->in_f != 0 || chunk_of(a) % a.quant->in_f != 0)
+      throw std::invalid_argument("OffloadEngine: chunks of a quantized weight must be whole rows");
+  }
+  if (is_resident(a.pid)) return step_resident(a, res_[a.pid]);
+  const bool nvfp4 = a.quant != nullptr && a.quant->format == kQNVFP4;
+  if (nvfp4 && a.master_copy == nullptr)
+    throw std::invalid_argument("OffloadEngine: an NVFP4 step needs master_copy");
+  const int64_t C = chunk_of(a);
   const size_t xb = elem_extra_bytes(k.mode);
   bool waited = false;
+  // the step kernels of an NVFP4 weight combine max|master| with atomicMax: start from zero
+  if (nvfp4 && k.amax_out != nullptr) check(cudaMemsetAsync(k.amax_out, 0, sizeof(float), compute_), "clear amax");
   for (int64_t off = 0; off < k.n; off += C) {
     const int64_t len = (k.n - off < C) ? (k.n - off) : C;
     Entry* e = nullptr;
@@ -453,10 +566,11 @@ void OffloadEngine::staged_step(const StagedStepArgs& a) {
     else if (k.g) { c.g = (const char*)k.g + 2 * off; c.g2 = nullptr; }
     else { c.g = e->g; c.g2 = nullptr; }
     c.m = e->m; c.v = e->v; c.extra = xb ? e->x : nullptr;
+    c.extra_copy = nvfp4 ? (char*)a.master_copy + 4 * off : nullptr;
     c.max_ctas = opt_.max_ctas;
     for (int j = 0; j < k.n_g_peers; ++j) c.g_peers[j] = (const char*)k.g_peers[j] + 2 * off;
     for (int j = 0; j < k.n_p_peers; ++j) c.p_peers[j] = (char*)k.p_peers[j] + 2 * off;
-    check(launch_adam_step(c, compute_), "adam_step");
+    check(launch_chunk(a, c, off), "adam_step");
     check(cudaEventRecord(e->k_done, compute_), "record");
 
     WbJob j;
@@ -476,6 +590,7 @@ void OffloadEngine::staged_step(const StagedStepArgs& a) {
     j.pid = (last && a.pid >= 0 && a.pid < (int)host_ready_.size()) ? a.pid : -1;
     submit_writeback(j);
   }
+  return nvfp4 ? a.master_copy : nullptr;
 }
 
 void OffloadEngine::staged_grad_to_host(int pid, void* host_grad, const void* dev_grad, int64_t n,
@@ -531,6 +646,11 @@ void OffloadEngine::staged_grad_to_host(int pid, void* host_grad, const void* de
     check(cudaEventRecord(grad_ready_[pid], d2h_), "record grad_ready");
     grad_ready_set_[pid] = 1;
   }
+}
+
+void OffloadEngine::wait_host_grad(int pid) {
+  if (pid >= 0 && pid < (int)grad_ready_.size() && grad_ready_set_[pid])
+    check(cudaStreamWaitEvent(compute_, grad_ready_[pid], 0), "wait grad_ready");
 }
 
 void OffloadEngine::join(cudaStream_t stream) {

@@ -32,6 +32,7 @@
 #include <thread>
 #include <vector>
 
+#include "adam_quant.h"
 #include "adam_step.h"
 
 namespace oab {
@@ -56,6 +57,17 @@ struct StagedStepArgs {
   const void* host_grad = nullptr;  // optional host-resident accumulated gradient
                                     // (added to k.g as the kernel's second term, or used
                                     // alone when k.g == nullptr)
+  int64_t chunk = 0;                // elements per chunk of this tensor (0: the engine's
+                                    // default); a multiple of in_f for quantized weights,
+                                    // whose chunks must be whole rows
+  // Quantized weight (fp32_master): the updated master is re-quantized and the packed
+  // rows are stored into every replica in the same pass (adam_quant.h).  quant->row0 is
+  // the first row of this tensor (or shard) within the weight.
+  const QuantPushArgs* quant = nullptr;
+  // NVFP4 only (its tensor scale needs the whole updated weight first): k.amax_out
+  // receives max|master| and the updated master is kept on the device for the quantize
+  // pass that follows, in this buffer of k.n floats unless the tensor is resident.
+  void* master_copy = nullptr;
 };
 
 class OffloadEngine {
@@ -70,8 +82,23 @@ class OffloadEngine {
 
   // Adam step of one tensor through the staging buffer.  The caller has already
   // made the compute stream wait for the gradient producer.  Chunks that
-  // prefetch() already brought in are consumed in place.
-  void staged_step(const StagedStepArgs& a);
+  // prefetch() already brought in are consumed in place.  Returns the device address
+  // at which the updated fp32 master of the whole tensor can be read by later work on
+  // the compute stream when a.quant is NVFP4 (a.master_copy, or the resident copy),
+  // nullptr otherwise.
+  void* staged_step(const StagedStepArgs& a);
+
+  // Resident tensors.  The front of the staging buffer can be given to the state of
+  // chosen tensors for good: it is loaded once, every step runs as ONE launch on the
+  // whole tensor and is followed by one write-back copy per state tensor, and no
+  // byte of it crosses the host link towards the device again.  The host copy stays
+  // current (it is written after every step) and authoritative (discard_prefetched()
+  // makes the engine load it again).  Call before the first step or prefetch; returns
+  // false, changing nothing, when the state does not fit in front of a ring of at
+  // least min_ring_bytes.
+  bool make_resident(int pid, int mode, int64_t n);
+  bool is_resident(int pid) const { return pid >= 0 && pid < (int)res_.size() && res_[pid].on; }
+  size_t resident_bytes() const { return res_bytes_; }
 
   // Early H2D: copies the host state (and host gradient, if given) of the tensor
   // into free staging space, chunk by chunk from `from_off`, before its gradient
@@ -98,6 +125,7 @@ class OffloadEngine {
     int mode = 0;
     int64_t n = 0;
     void *m = nullptr, *v = nullptr, *extra = nullptr;
+    int64_t chunk = 0;  // as StagedStepArgs::chunk
   };
   void start_prefetch(std::vector<PrefetchItem> items, int max_inflight);
   void stop_prefetch();
@@ -109,6 +137,10 @@ class OffloadEngine {
   // the result into *sumsq_out (device pointer).  first == true: plain D2H copy.
   void staged_grad_to_host(int pid, void* host_grad, const void* dev_grad, int64_t n, bool first,
                            float* sumsq_out, float* scratch);
+
+  // Makes the compute stream wait for the last D2H copy into the host gradient buffer of
+  // tensor `pid` (for kernels that read that pinned buffer directly).
+  void wait_host_grad(int pid);
 
   // Makes `stream` wait until every transfer/kernel enqueued so far has finished.
   void join(cudaStream_t stream);
@@ -151,6 +183,19 @@ class OffloadEngine {
     cudaEvent_t k_done = nullptr, free_ev = nullptr;
     int pid = -1;  // >= 0: last chunk of that tensor, record host_ready_[pid] after it
   };
+  // State of one tensor kept in the front part of the staging buffer.
+  struct Resident {
+    bool on = false, loaded = false;
+    int mode = 0;
+    int64_t n = 0;
+    char *m = nullptr, *v = nullptr, *x = nullptr;
+    cudaEvent_t h2d_done = nullptr, k_done = nullptr, free_ev = nullptr;
+    Entry wb;  // stands in for a ring chunk in the write-back job
+  };
+  void load_resident(const StagedStepArgs& a, Resident& r);
+  void* step_resident(const StagedStepArgs& a, Resident& r);
+  cudaError_t launch_chunk(const StagedStepArgs& a, const AdamStepArgs& c, int64_t off);
+  int64_t chunk_of(const StagedStepArgs& a) const { return a.chunk > 0 ? a.chunk : opt_.chunk_elems; }
   int64_t prefetch_impl(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks,
                         int max_inflight, bool* full);
   void discard_impl();
@@ -170,6 +215,8 @@ class OffloadEngine {
   EngineOptions opt_;
   char* ring_ = nullptr;
   size_t ring_bytes_ = 0, head_ = 0;
+  std::vector<Resident> res_;
+  size_t res_bytes_ = 0;  // taken from the front of the workspace; the ring starts behind it
   std::list<Entry> live_;        // allocation order, oldest first
   std::deque<Entry*> loaded_;    // prefetched, not yet consumed (consumption order)
   std::deque<Entry*> inflight_;  // prefetch copies possibly still running

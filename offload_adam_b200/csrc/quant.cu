@@ -17,106 +17,14 @@
 // loads/stores; block statistics are combined with warp shuffles.  The E2M1
 // conversions use the Blackwell cvt instructions (cvt.rn.satfinite.e2m1x2.f32,
 // cvt.rn.f16x2.e2m1x2).
-#include <cuda_fp16.h>
-#include <cuda_fp8.h>
-
-#include "common.cuh"
 #include "quant.h"
+#include "quant_math.cuh"
 
 namespace oab {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr float kEps = 1e-12f;
-
-// ------------------------------------------------------------------ element I/O
-template <typename T> struct Elem;
-template <> struct Elem<float> {
-  static __device__ __forceinline__ void load16(const float* p, float (&x)[16]) {
-    V8 a = ld32_stream(p), b = ld32_stream(p + 8);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { x[i] = __uint_as_float(a.w[i]); x[8 + i] = __uint_as_float(b.w[i]); }
-  }
-  static __device__ __forceinline__ void store16(float* p, const float (&x)[16]) {
-    V8 a, b;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { a.w[i] = __float_as_uint(x[i]); b.w[i] = __float_as_uint(x[8 + i]); }
-    st32_stream(p, a); st32_stream(p + 8, b);
-  }
-  static __device__ __forceinline__ float to_f32(float v) { return v; }
-  static __device__ __forceinline__ float from_f32(float v) { return v; }
-};
-template <> struct Elem<__nv_bfloat16> {
-  static __device__ __forceinline__ void load16(const __nv_bfloat16* p, float (&x)[16]) {
-    V8 a = ld32_stream(p);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { x[2 * i] = __uint_as_float(a.w[i] << 16); x[2 * i + 1] = __uint_as_float(a.w[i] & 0xffff0000u); }
-  }
-  static __device__ __forceinline__ void store16(__nv_bfloat16* p, const float (&x)[16]) {
-    V8 a;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) a.w[i] = f32_to_bf16_rne_bits(x[2 * i]) | (f32_to_bf16_rne_bits(x[2 * i + 1]) << 16);
-    st32_stream(p, a);
-  }
-  static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
-  static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
-};
-template <> struct Elem<__half> {
-  static __device__ __forceinline__ void load16(const __half* p, float (&x)[16]) {
-    V8 a = ld32_stream(p);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      __half2 h = *reinterpret_cast<__half2*>(&a.w[i]);
-      float2 f = __half22float2(h);
-      x[2 * i] = f.x; x[2 * i + 1] = f.y;
-    }
-  }
-  static __device__ __forceinline__ void store16(__half* p, const float (&x)[16]) {
-    V8 a;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      __half2 h = __halves2half2(__float2half_rn(x[2 * i]), __float2half_rn(x[2 * i + 1]));
-      a.w[i] = *reinterpret_cast<uint32_t*>(&h);
-    }
-    st32_stream(p, a);
-  }
-  static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
-  static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
-};
-
-__device__ __forceinline__ float amax16(const float (&x)[16]) {
-  float m = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(x[i]));
-  return m;
-}
-// max over groups of `lanes` consecutive lanes (power of two)
-__device__ __forceinline__ float group_max(float v, int lanes) {
-  for (int o = lanes >> 1; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-__device__ __forceinline__ float rcp_rn(float x) { return __frcp_rn(x); }
-
-__device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
-  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
-  return __half2float(*reinterpret_cast<__half*>(&h));
-}
-__device__ __forceinline__ uint8_t f32_to_e4m3(float x) {
-  return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
-}
-// two fp32 -> one byte of E2M1 codes (lo in the low nibble), RNE, saturating
-__device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
-  uint32_t r;
-  asm("{\n .reg .b8 t;\n cvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n cvt.u32.u8 %0, t;\n}" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-// one byte of E2M1 codes -> two fp32 (low nibble first)
-__device__ __forceinline__ float2 e2m1x2_to_f32(uint32_t byte) {
-  uint32_t r;
-  asm("{\n .reg .b8 t;\n cvt.u8.u32 t, %1;\n cvt.rn.f16x2.e2m1x2 %0, t;\n}" : "=r"(r) : "r"(byte));
-  __half2 h = *reinterpret_cast<__half2*>(&r);
-  return __half22float2(h);
-}
+using namespace qm;
 
 // ------------------------------------------------------------------------ amax
 template <typename T>
@@ -136,30 +44,46 @@ __global__ void __launch_bounds__(kThreads) absmax_kernel(const T* x, int64_t n,
 }
 
 // ----------------------------------------------------------------------- NVFP4
-// one thread per 16-element block; global_scale[0] is written by thread 0
-template <typename T>
+// One thread per 16-element block.  The four scale bytes of four neighbouring blocks
+// are combined with shuffles and leave as one 32-bit store; global_scale[0] is written
+// by thread 0.  FAKE: instead of the payload, write the de-quantized values to `out`.
+template <typename T, bool FAKE>
 __global__ void __launch_bounds__(kThreads)
 nvfp4_quantize_kernel(const T* x, int64_t nblocks, const float* amax, uint8_t* packed, uint8_t* scales,
-                      float* global_scale_out) {
-  const float tensor_amax = fmaxf(*amax, kEps);
-  const float global = __fdiv_rn(tensor_amax, 448.0f * 6.0f);
-  const float inv_global = rcp_rn(fmaxf(global, kEps));
-  if (blockIdx.x == 0 && threadIdx.x == 0) *global_scale_out = global;
-  for (int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x; b < nblocks; b += (int64_t)gridDim.x * kThreads) {
+                      float* global_scale_out, int scale_words_ok, T* out) {
+  float global, inv_global;
+  nvfp4_global(*amax, global, inv_global);
+  if (!FAKE && blockIdx.x == 0 && threadIdx.x == 0) *global_scale_out = global;
+  const int lane = threadIdx.x & 31;
+  // whole warps iterate together so that every shuffle has its partners
+  for (int64_t base = (int64_t)blockIdx.x * kThreads + (threadIdx.x & ~31); base < nblocks;
+       base += (int64_t)gridDim.x * kThreads) {
+    const int64_t b = base + lane;
+    const bool live = b < nblocks;
     float e[16];
-    Elem<T>::load16(x + b * 16, e);
-    const float bamax = fmaxf(amax16(e), kEps);
-    const uint8_t s8 = f32_to_e4m3(__fmul_rn(__fdiv_rn(bamax, 6.0f), inv_global));
-    scales[b] = s8;
-    const float eff = __fmul_rn(e4m3_to_f32(s8), global);
-    const float inv_eff = rcp_rn(fmaxf(eff, kEps));
+    uint8_t s8 = 0;
     uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      w0 |= e2m1x2(__fmul_rn(e[2 * i], inv_eff), __fmul_rn(e[2 * i + 1], inv_eff)) << (8 * i);
-      w1 |= e2m1x2(__fmul_rn(e[8 + 2 * i], inv_eff), __fmul_rn(e[9 + 2 * i], inv_eff)) << (8 * i);
+    if (live) {
+      Elem<T>::load16(x + b * 16, e);
+      nvfp4_pack16(e, global, inv_global, s8, w0, w1);
     }
+    if (FAKE) {
+      if (live) {
+        nvfp4_unpack16(w0, w1, __fmul_rn(e4m3_to_f32(s8), global), e);
+        Elem<T>::store16(out + b * 16, e);
+      }
+      continue;
+    }
+    uint32_t s32 = s8;
+    s32 |= __shfl_down_sync(0xffffffffu, (uint32_t)s8, 1) << 8;
+    s32 |= __shfl_down_sync(0xffffffffu, s32, 2) << 16;
+    if (!live) continue;
     *reinterpret_cast<uint2*>(packed + b * 8) = make_uint2(w0, w1);
+    if (scale_words_ok && b + 3 < nblocks) {
+      if ((lane & 3) == 0) *reinterpret_cast<uint32_t*>(scales + b) = s32;
+    } else {
+      scales[b] = s8;
+    }
   }
 }
 
@@ -170,51 +94,18 @@ nvfp4_dequantize_kernel(const uint8_t* packed, const uint8_t* scales, const floa
   const float global = *global_scale;
   for (int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x; b < nblocks; b += (int64_t)gridDim.x * kThreads) {
     const uint2 w = *reinterpret_cast<const uint2*>(packed + b * 8);
-    const float eff = __fmul_rn(e4m3_to_f32(scales[b]), global);
     float e[16];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 a = e2m1x2_to_f32((w.x >> (8 * i)) & 0xffu);
-      float2 c = e2m1x2_to_f32((w.y >> (8 * i)) & 0xffu);
-      e[2 * i] = __fmul_rn(a.x, eff); e[2 * i + 1] = __fmul_rn(a.y, eff);
-      e[8 + 2 * i] = __fmul_rn(c.x, eff); e[9 + 2 * i] = __fmul_rn(c.y, eff);
-    }
+    nvfp4_unpack16(w.x, w.y, __fmul_rn(e4m3_to_f32(scales[b]), global), e);
     Elem<T>::store16(out + b * 16, e);
   }
 }
 
 // ------------------------------------------------------------------------- NF4
-__constant__ float kNF4[16] = {
-    -1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
-    -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
-    0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
-    0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
-
-// index of the nearest codebook entry; among equal distances the lowest index wins
-// (the rule of a sequential scan with a strict '<').  A 4-step bisection on the
-// midpoints finds a candidate, its two neighbours settle rounding and ties.
-__device__ __forceinline__ int nf4_nearest(float x, const float* lut) {
-  int lo = 0;
-#pragma unroll
-  for (int step = 8; step > 0; step >>= 1) {
-    int mid = lo + step;  // compare against the midpoint between mid-1 and mid
-    float mp = 0.5f * (lut[mid - 1] + lut[mid]);
-    lo = (x > mp) ? mid : lo;
-  }
-  int best = lo > 0 ? lo - 1 : lo;
-  float bd = fabsf(__fsub_rn(x, lut[best]));
-  int hi = lo < 15 ? lo + 1 : lo;
-  for (int c = best + 1; c <= hi; ++c) {
-    float d = fabsf(__fsub_rn(x, lut[c]));
-    if (d < bd) { bd = d; best = c; }
-  }
-  return best;
-}
-
-// one thread per 16 elements; lanes_per_block = blocksize / 16 (power of two <= 32)
-template <typename T>
+// one thread per 16 elements; lanes_per_block = blocksize / 16 (power of two <= 32).
+// FAKE: write the de-quantized values to `out` instead of the payload.
+template <typename T, bool FAKE>
 __global__ void __launch_bounds__(kThreads)
-nf4_quantize_kernel(const T* x, int64_t nchunks, int lanes_per_block, uint8_t* packed, float* absmax) {
+nf4_quantize_kernel(const T* x, int64_t nchunks, int lanes_per_block, uint8_t* packed, float* absmax, T* out) {
   __shared__ float lut[16];
   if (threadIdx.x < 16) lut[threadIdx.x] = kNF4[threadIdx.x];
   __syncthreads();
@@ -230,16 +121,14 @@ nf4_quantize_kernel(const T* x, int64_t nchunks, int lanes_per_block, uint8_t* p
     }
     const float am = group_max(amax16(e), lanes_per_block);
     if (!live) continue;
-    if ((c % lanes_per_block) == 0) absmax[c / lanes_per_block] = am;
-    const float inv = rcp_rn(fmaxf(am, kEps));
-    uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint32_t b0 = (nf4_nearest(__fmul_rn(e[2 * i], inv), lut) << 4) | nf4_nearest(__fmul_rn(e[2 * i + 1], inv), lut);
-      uint32_t b1 = (nf4_nearest(__fmul_rn(e[8 + 2 * i], inv), lut) << 4) | nf4_nearest(__fmul_rn(e[9 + 2 * i], inv), lut);
-      w0 |= b0 << (8 * i);
-      w1 |= b1 << (8 * i);
+    uint32_t w0, w1;
+    nf4_pack16(e, rcp_rn(fmaxf(am, kEps)), lut, w0, w1);
+    if (FAKE) {
+      nf4_unpack16(w0, w1, am, lut, e);
+      Elem<T>::store16(out + c * 16, e);
+      continue;
     }
+    if ((c % lanes_per_block) == 0) absmax[c / lanes_per_block] = am;
     *reinterpret_cast<uint2*>(packed + c * 8) = make_uint2(w0, w1);
   }
 }
@@ -252,64 +141,73 @@ nf4_dequantize_kernel(const uint8_t* packed, const float* absmax, int64_t nchunk
   __syncthreads();
   for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < nchunks; c += (int64_t)gridDim.x * kThreads) {
     const uint2 w = *reinterpret_cast<const uint2*>(packed + c * 8);
-    const float am = absmax[c / lanes_per_block];
     float e[16];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint32_t b0 = (w.x >> (8 * i)) & 0xffu, b1 = (w.y >> (8 * i)) & 0xffu;
-      e[2 * i] = __fmul_rn(lut[b0 >> 4], am); e[2 * i + 1] = __fmul_rn(lut[b0 & 15], am);
-      e[8 + 2 * i] = __fmul_rn(lut[b1 >> 4], am); e[9 + 2 * i] = __fmul_rn(lut[b1 & 15], am);
-    }
+    nf4_unpack16(w.x, w.y, absmax[c / lanes_per_block], lut, e);
     Elem<T>::store16(out + c * 16, e);
   }
 }
 
 // ------------------------------------------------------------------------ int8
-// one block per row; the second pass re-reads the row, which the first pass left in L2
-template <typename T, typename S>
+// one block per row; the second pass re-reads the row, which the first pass left in L2.
+// FAKE: write the de-quantized row to `out` (dtype T) instead of the payload.
+template <typename T, typename S, bool FAKE>
 __global__ void __launch_bounds__(kThreads)
-int8_quantize_kernel(const T* x, int64_t in_f, int8_t* q, S* scales) {
+int8_quantize_kernel(const T* x, int64_t out_f, int64_t in_f, int8_t* q, S* scales, T* out) {
   __shared__ float red[kThreads / 32];
-  __shared__ float s_inv;
-  const int64_t row = blockIdx.x;
-  const T* xr = x + row * in_f;
-  float m = 0.f;
-  const bool vec = (in_f % 16 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 31u) == 0);
-  if (vec) {
-    for (int64_t v = threadIdx.x; v < (in_f >> 4); v += kThreads) {
-      float e[16];
-      Elem<T>::load16(xr + v * 16, e);
-      m = fmaxf(m, amax16(e));
-    }
-  } else {
-    for (int64_t i = threadIdx.x; i < in_f; i += kThreads) m = fmaxf(m, fabsf(Elem<T>::to_f32(xr[i])));
-  }
-  float bm = block_max<kThreads>(m, red);
-  if (threadIdx.x == 0) {
-    const float scale = __fdiv_rn(bm, 127.0f);
-    scales[row] = Elem<S>::from_f32(scale);
-    s_inv = rcp_rn(fmaxf(scale, kEps));
-  }
-  __syncthreads();
-  const float inv = s_inv;
-  int8_t* qr = q + row * in_f;
-  if (vec && ((reinterpret_cast<uintptr_t>(qr) & 15u) == 0)) {
-    for (int64_t v = threadIdx.x; v < (in_f >> 4); v += kThreads) {
-      float e[16];
-      Elem<T>::load16(xr + v * 16, e);
-      uint32_t w[4] = {0, 0, 0, 0};
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float r = fminf(fmaxf(rintf(__fmul_rn(e[i], inv)), -128.f), 127.f);
-        w[i >> 2] |= ((uint32_t)(uint8_t)(int8_t)(int)r) << (8 * (i & 3));
+  __shared__ float s_inv, s_scale;
+  for (int64_t row = blockIdx.x; row < out_f; row += gridDim.x) {
+    const T* xr = x + row * in_f;
+    float m = 0.f;
+    const bool vec = (in_f % 16 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 31u) == 0);
+    if (vec) {
+      for (int64_t v = threadIdx.x; v < (in_f >> 4); v += kThreads) {
+        float e[16];
+        Elem<T>::load16(xr + v * 16, e);
+        m = fmaxf(m, amax16(e));
       }
-      *reinterpret_cast<uint4*>(qr + v * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      for (int64_t i = threadIdx.x; i < in_f; i += kThreads) m = fmaxf(m, fabsf(Elem<T>::to_f32(xr[i])));
     }
-  } else {
-    for (int64_t i = threadIdx.x; i < in_f; i += kThreads) {
-      float r = fminf(fmaxf(rintf(__fmul_rn(Elem<T>::to_f32(xr[i]), inv)), -128.f), 127.f);
-      qr[i] = (int8_t)(int)r;
+    float bm = block_max<kThreads>(m, red);
+    if (threadIdx.x == 0) {
+      const float scale = __fdiv_rn(bm, 127.0f);
+      if (!FAKE) scales[row] = Elem<S>::from_f32(scale);
+      s_scale = stored_scale<S>(scale);
+      s_inv = rcp_rn(fmaxf(scale, kEps));
     }
+    __syncthreads();
+    const float inv = s_inv, sc = s_scale;
+    if (FAKE) {
+      T* orow = out + row * in_f;
+      const bool ovec = vec && ((reinterpret_cast<uintptr_t>(orow) & 31u) == 0);
+      for (int64_t v = threadIdx.x; v < ((in_f + 15) >> 4); v += kThreads) {
+        const int64_t left = in_f - v * 16;
+        if (ovec) {
+          float e[16];
+          Elem<T>::load16(xr + v * 16, e);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) e[i] = round_like_dequant<T, S>(__fmul_rn((float)int8_round(e[i], inv), sc));
+          Elem<T>::store16(orow + v * 16, e);
+        } else {
+          for (int i = 0; i < 16 && i < left; ++i) {
+            const float xv = Elem<T>::to_f32(xr[v * 16 + i]);
+            orow[v * 16 + i] = Elem<T>::from_f32(round_like_dequant<T, S>(__fmul_rn((float)int8_round(xv, inv), sc)));
+          }
+        }
+      }
+    } else {
+      int8_t* qr = q + row * in_f;
+      if (vec && ((reinterpret_cast<uintptr_t>(qr) & 15u) == 0)) {
+        for (int64_t v = threadIdx.x; v < (in_f >> 4); v += kThreads) {
+          float e[16];
+          Elem<T>::load16(xr + v * 16, e);
+          *reinterpret_cast<uint4*>(qr + v * 16) = int8_pack16(e, inv);
+        }
+      } else {
+        for (int64_t i = threadIdx.x; i < in_f; i += kThreads) qr[i] = (int8_t)int8_round(Elem<T>::to_f32(xr[i]), inv);
+      }
+    }
+    __syncthreads();  // s_inv / s_scale are rewritten for the next row
   }
 }
 
@@ -338,83 +236,64 @@ int8_dequantize_kernel(const int8_t* q, const S* scales, int64_t out_f, int64_t 
 }
 
 // ------------------------------------------------------------------------ int4
-// Tile = 32 rows x 128 columns.  A warp quantizes 4 rows; each lane owns 4 columns.
-// Packed words go through shared memory so that the (in_f/8, out_f) layout is
-// written with 128-byte rows-contiguous stores.
+// Tile = 32 rows x 128 columns (see Int4Tile): every thread moves 16 consecutive
+// elements of a row with one (bf16/fp16) or two (fp32) 256-bit accesses; the packed
+// words are transposed through shared memory.
 template <typename T, typename S>
 __global__ void __launch_bounds__(kThreads)
-int4_quantize_kernel(const T* x, int64_t out_f, int64_t in_f, int group, int32_t* qweight, S* scales) {
-  __shared__ int32_t tile[16][33];
-  __shared__ float tscale[4][33];
+int4_quantize_kernel(const T* x, int64_t out_f, int64_t in_f, int group, int32_t* qweight, S* scales, int aligned) {
+  __shared__ Int4Tile sm;
   const int64_t row0 = (int64_t)blockIdx.x * 32;
   const int64_t col0 = (int64_t)blockIdx.y * 128;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int lanes_per_group = group / 4;
-  const int groups_per_tile = 128 / group;
+  const int lr = threadIdx.x >> 3, seg = threadIdx.x & 7;
+  float e[16];
+  if (row0 + lr < out_f) load16_any(x + (row0 + lr) * in_f + col0 + seg * 16, e, aligned != 0);
+  else {
 #pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const int lr = warp * 4 + r;
-    const int64_t row = row0 + lr;
-    float e[4] = {0.f, 0.f, 0.f, 0.f};
-    if (row < out_f) {
-      const T* src = x + row * in_f + col0 + lane * 4;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) e[i] = Elem<T>::to_f32(src[i]);
-    }
-    float am = fmaxf(fmaxf(fabsf(e[0]), fabsf(e[1])), fmaxf(fabsf(e[2]), fabsf(e[3])));
-    am = group_max(am, lanes_per_group);
-    const float scale = __fmul_rn(am, 0.125f);
-    const float inv = rcp_rn(fmaxf(scale, kEps));
-    uint32_t nib = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float q = fminf(fmaxf(rintf(__fmul_rn(e[i], inv)), -8.f), 7.f);
-      nib |= ((uint32_t)((int)q + 8) & 0xfu) << (4 * i);
-    }
-    const uint32_t other = __shfl_down_sync(0xffffffffu, nib, 1);
-    if ((lane & 1) == 0) tile[lane >> 1][lr] = (int32_t)(nib | (other << 16));
-    if ((lane % lanes_per_group) == 0) tscale[lane / lanes_per_group][lr] = scale;
+    for (int i = 0; i < 16; ++i) e[i] = 0.f;
   }
+  int4_tile_quantize(e, group, sm);
   __syncthreads();
-  // 16 packed rows x 32 output rows
-  for (int i = threadIdx.x; i < 16 * 32; i += kThreads) {
-    const int k = i >> 5, lr = i & 31;
-    if (row0 + lr < out_f) qweight[(col0 / 8 + k) * out_f + row0 + lr] = tile[k][lr];
-  }
-  for (int i = threadIdx.x; i < groups_per_tile * 32; i += kThreads) {
-    const int gi = i >> 5, lr = i & 31;
-    if (row0 + lr < out_f) scales[(col0 / group + gi) * out_f + row0 + lr] = Elem<S>::from_f32(tscale[gi][lr]);
-  }
+  const int64_t left = out_f - row0;
+  int4_tile_store<S>(sm, out_f, row0, left < 32 ? (int)left : 32, col0, group, qweight, scales);
 }
 
 template <typename S>
 __global__ void __launch_bounds__(kThreads)
-int4_dequantize_kernel(const int32_t* qweight, const S* scales, int64_t out_f, int64_t in_f, int group, S* out) {
-  __shared__ int32_t tile[16][33];
-  __shared__ float tscale[4][33];
+int4_dequantize_kernel(const int32_t* qweight, const S* scales, int64_t out_f, int64_t in_f, int group, S* out, int aligned) {
+  __shared__ Int4Tile sm;
   const int64_t row0 = (int64_t)blockIdx.x * 32;
   const int64_t col0 = (int64_t)blockIdx.y * 128;
-  const int groups_per_tile = 128 / group;
-  for (int i = threadIdx.x; i < 16 * 32; i += kThreads) {
-    const int k = i >> 5, lr = i & 31;
-    tile[k][lr] = (row0 + lr < out_f) ? qweight[(col0 / 8 + k) * out_f + row0 + lr] : 0;
-  }
-  for (int i = threadIdx.x; i < groups_per_tile * 32; i += kThreads) {
-    const int gi = i >> 5, lr = i & 31;
-    tscale[gi][lr] = (row0 + lr < out_f) ? Elem<S>::to_f32(scales[(col0 / group + gi) * out_f + row0 + lr]) : 0.f;
-  }
+  const int64_t left = out_f - row0;
+  int4_tile_load<S>(sm, out_f, row0, left < 32 ? (int)left : 32, col0, group, qweight, scales);
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lr = threadIdx.x >> 3, seg = threadIdx.x & 7;
+  if (row0 + lr >= out_f) return;
+  float e[16];
+  int4_unpack16((uint32_t)sm.words[seg * 2][lr], (uint32_t)sm.words[seg * 2 + 1][lr], sm.scale[(seg * 16) / group][lr], e);
+  store16_any(out + (row0 + lr) * in_f + col0 + seg * 16, e, aligned != 0);
+}
+
+// dq(q(x)) for int4 needs no transposition: one thread per 16 elements of a row, a
+// group is 2, 4 or 8 consecutive lanes
+template <typename T, typename S>
+__global__ void __launch_bounds__(kThreads)
+int4_fake_quant_kernel(const T* x, int64_t nchunks, int lanes_per_group, T* out) {
+  const int64_t total = (nchunks + 31) / 32 * 32;
+  for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < total; c += (int64_t)gridDim.x * kThreads) {
+    float e[16];
+    const bool live = c < nchunks;
+    if (live) Elem<T>::load16(x + c * 16, e);
+    else {
 #pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const int lr = warp * 4 + r;
-    const int64_t row = row0 + lr;
-    if (row >= out_f) continue;
-    const uint32_t w = (uint32_t)tile[lane >> 1][lr] >> (16 * (lane & 1));
-    const float s = tscale[(lane * 4) / group][lr];
-    S* dst = out + row * in_f + col0 + lane * 4;
+      for (int i = 0; i < 16; ++i) e[i] = 0.f;
+    }
+    const float scale = __fmul_rn(group_max(amax16(e), lanes_per_group), 0.125f);
+    if (!live) continue;
+    const float inv = rcp_rn(fmaxf(scale, kEps)), sc = stored_scale<S>(scale);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) dst[i] = Elem<S>::from_f32(__fmul_rn((float)((int)((w >> (4 * i)) & 0xfu) - 8), s));
+    for (int i = 0; i < 16; ++i) e[i] = round_like_dequant<T, S>(__fmul_rn((float)int4_round(e[i], inv), sc));
+    Elem<T>::store16(out + c * 16, e);
   }
 }
 
@@ -447,17 +326,27 @@ cudaError_t launch_absmax(const void* x, int dtype, int64_t n, float* out, cudaS
   return cudaGetLastError();
 }
 
+namespace {
+bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
+}  // namespace
+
 cudaError_t launch_nvfp4_quantize(const void* x, int dtype, int64_t numel, const float* amax,
                                   uint8_t* packed, uint8_t* scales, float* global_scale, cudaStream_t st) {
   const int64_t nb = numel / 16;
+  if (nb <= 0) return cudaSuccess;
+  if (!aligned32(x) || (reinterpret_cast<uintptr_t>(packed) & 7u)) return cudaErrorInvalidValue;
+  const int words_ok = (reinterpret_cast<uintptr_t>(scales) & 3u) == 0;
   count_launch();
-  OAB_DISPATCH_IN(dtype, nvfp4_quantize_kernel<T><<<grid_for(nb), kThreads, 0, st>>>((const T*)x, nb, amax, packed, scales, global_scale));
+  OAB_DISPATCH_IN(dtype, nvfp4_quantize_kernel<T, false><<<grid_for(nb), kThreads, 0, st>>>(
+      (const T*)x, nb, amax, packed, scales, global_scale, words_ok, nullptr));
   return cudaGetLastError();
 }
 
 cudaError_t launch_nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, const float* global_scale,
                                     int64_t numel, void* out, int dtype, cudaStream_t st) {
   const int64_t nb = numel / 16;
+  if (nb <= 0) return cudaSuccess;
+  if (!aligned32(out) || (reinterpret_cast<uintptr_t>(packed) & 7u)) return cudaErrorInvalidValue;
   count_launch();
   OAB_DISPATCH_IN(dtype, nvfp4_dequantize_kernel<T><<<grid_for(nb), kThreads, 0, st>>>(packed, scales, global_scale, nb, (T*)out));
   return cudaGetLastError();
@@ -466,14 +355,19 @@ cudaError_t launch_nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales
 cudaError_t launch_nf4_quantize(const void* x, int dtype, int64_t numel, int blocksize, uint8_t* packed,
                                 float* absmax, cudaStream_t st) {
   const int64_t nc = numel / 16;
+  if (nc <= 0) return cudaSuccess;
+  if (!aligned32(x) || (reinterpret_cast<uintptr_t>(packed) & 7u)) return cudaErrorInvalidValue;
   count_launch();
-  OAB_DISPATCH_IN(dtype, nf4_quantize_kernel<T><<<grid_for(nc), kThreads, 0, st>>>((const T*)x, nc, blocksize / 16, packed, absmax));
+  OAB_DISPATCH_IN(dtype, nf4_quantize_kernel<T, false><<<grid_for(nc), kThreads, 0, st>>>(
+      (const T*)x, nc, blocksize / 16, packed, absmax, nullptr));
   return cudaGetLastError();
 }
 
 cudaError_t launch_nf4_dequantize(const uint8_t* packed, const float* absmax, int64_t numel, int blocksize,
                                   void* out, int dtype, cudaStream_t st) {
   const int64_t nc = numel / 16;
+  if (nc <= 0) return cudaSuccess;
+  if (!aligned32(out) || (reinterpret_cast<uintptr_t>(packed) & 7u)) return cudaErrorInvalidValue;
   count_launch();
   OAB_DISPATCH_IN(dtype, nf4_dequantize_kernel<T><<<grid_for(nc), kThreads, 0, st>>>(packed, absmax, nc, blocksize / 16, (T*)out));
   return cudaGetLastError();
@@ -482,14 +376,16 @@ cudaError_t launch_nf4_dequantize(const uint8_t* packed, const float* absmax, in
 cudaError_t launch_int8_quantize(const void* x, int dtype, int64_t out_f, int64_t in_f, int8_t* q,
                                  void* scales, int scale_dtype, cudaStream_t st) {
   if (out_f <= 0) return cudaSuccess;
+  const unsigned grid = (unsigned)(out_f < (int64_t)kNumSMs * 16 ? out_f : (int64_t)kNumSMs * 16);
   count_launch();
   OAB_DISPATCH_IN(dtype, OAB_DISPATCH_SCALE(scale_dtype,
-      int8_quantize_kernel<T, S><<<(unsigned)out_f, kThreads, 0, st>>>((const T*)x, in_f, q, (S*)scales)));
+      int8_quantize_kernel<T, S, false><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, q, (S*)scales, nullptr)));
   return cudaGetLastError();
 }
 
 cudaError_t launch_int8_dequantize(const int8_t* q, const void* scales, int scale_dtype, int64_t out_f,
                                    int64_t in_f, void* out, cudaStream_t st) {
+  if (out_f <= 0) return cudaSuccess;
   count_launch();
   OAB_DISPATCH_SCALE(scale_dtype, int8_dequantize_kernel<S><<<grid_for((out_f * in_f + 15) / 16), kThreads, 0, st>>>(q, (const S*)scales, out_f, in_f, (S*)out));
   return cudaGetLastError();
@@ -497,18 +393,63 @@ cudaError_t launch_int8_dequantize(const int8_t* q, const void* scales, int scal
 
 cudaError_t launch_int4_quantize(const void* x, int dtype, int64_t out_f, int64_t in_f, int group,
                                  int32_t* qweight, void* scales, int scale_dtype, cudaStream_t st) {
+  if (out_f <= 0) return cudaSuccess;
+  if (in_f % 128 != 0 || (group != 32 && group != 64 && group != 128)) return cudaErrorInvalidValue;
   dim3 grid((unsigned)((out_f + 31) / 32), (unsigned)(in_f / 128));
   count_launch();
   OAB_DISPATCH_IN(dtype, OAB_DISPATCH_SCALE(scale_dtype,
-      int4_quantize_kernel<T, S><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, group, qweight, (S*)scales)));
+      int4_quantize_kernel<T, S><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, group, qweight, (S*)scales, aligned32(x) ? 1 : 0)));
   return cudaGetLastError();
 }
 
 cudaError_t launch_int4_dequantize(const int32_t* qweight, const void* scales, int scale_dtype, int64_t out_f,
                                    int64_t in_f, int group, void* out, cudaStream_t st) {
+  if (out_f <= 0) return cudaSuccess;
+  if (in_f % 128 != 0 || (group != 32 && group != 64 && group != 128)) return cudaErrorInvalidValue;
   dim3 grid((unsigned)((out_f + 31) / 32), (unsigned)(in_f / 128));
   count_launch();
-  OAB_DISPATCH_SCALE(scale_dtype, int4_dequantize_kernel<S><<<grid, kThreads, 0, st>>>(qweight, (const S*)scales, out_f, in_f, group, (S*)out));
+  OAB_DISPATCH_SCALE(scale_dtype, int4_dequantize_kernel<S><<<grid, kThreads, 0, st>>>(qweight, (const S*)scales, out_f, in_f, group, (S*)out, aligned32(out) ? 1 : 0));
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ fake quantization
+cudaError_t launch_fake_quant(int format, const void* x, void* out, int dtype, int64_t out_f, int64_t in_f,
+                              int group, int scale_dtype, const float* tensor_amax, cudaStream_t st) {
+  const int64_t numel = out_f * in_f;
+  if (numel <= 0) return cudaSuccess;
+  count_launch();
+  switch (format) {
+    case kQNVFP4: {
+      if (in_f % 16 != 0 || tensor_amax == nullptr || !aligned32(x) || !aligned32(out)) return cudaErrorInvalidValue;
+      const int64_t nb = numel / 16;
+      OAB_DISPATCH_IN(dtype, nvfp4_quantize_kernel<T, true><<<grid_for(nb), kThreads, 0, st>>>(
+          (const T*)x, nb, tensor_amax, nullptr, nullptr, nullptr, 0, (T*)out));
+      break;
+    }
+    case kQNF4: {
+      if (group < 16 || group > 512 || (group & (group - 1)) || in_f % group != 0 || !aligned32(x) || !aligned32(out))
+        return cudaErrorInvalidValue;
+      const int64_t nc = numel / 16;
+      OAB_DISPATCH_IN(dtype, nf4_quantize_kernel<T, true><<<grid_for(nc), kThreads, 0, st>>>(
+          (const T*)x, nc, group / 16, nullptr, nullptr, (T*)out));
+      break;
+    }
+    case kQInt4: {
+      if ((group != 32 && group != 64 && group != 128) || in_f % group != 0 || !aligned32(x) || !aligned32(out))
+        return cudaErrorInvalidValue;
+      const int64_t nc = numel / 16;
+      OAB_DISPATCH_IN(dtype, OAB_DISPATCH_SCALE(scale_dtype,
+          int4_fake_quant_kernel<T, S><<<grid_for(nc), kThreads, 0, st>>>((const T*)x, nc, group / 16, (T*)out)));
+      break;
+    }
+    case kQInt8: {
+      const unsigned grid = (unsigned)(out_f < (int64_t)kNumSMs * 16 ? out_f : (int64_t)kNumSMs * 16);
+      OAB_DISPATCH_IN(dtype, OAB_DISPATCH_SCALE(scale_dtype,
+          int8_quantize_kernel<T, S, true><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, nullptr, nullptr, (T*)out)));
+      break;
+    }
+    default: return cudaErrorInvalidValue;
+  }
   return cudaGetLastError();
 }
 

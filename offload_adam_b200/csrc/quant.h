@@ -6,6 +6,7 @@
 namespace oab {
 
 enum QDtype : int { kF32 = 0, kBF16 = 1, kF16 = 2 };
+enum QFormat : int { kQNone = 0, kQNVFP4 = 1, kQNF4 = 2, kQInt4 = 3, kQInt8 = 4 };
 
 // out[0] = max(out[0], max |x|) (fp32 bits compared as unsigned); zero `out` first.
 cudaError_t launch_absmax(const void* x, int dtype, int64_t n, float* out, cudaStream_t st);
@@ -36,5 +37,14 @@ cudaError_t launch_int4_quantize(const void* x, int dtype, int64_t out_f, int64_
 cudaError_t launch_int4_dequantize(const int32_t* qweight, const void* scales, int scale_dtype,
                                    int64_t out_f, int64_t in_f, int group, void* out,
                                    cudaStream_t st);
+
+// out = dequantize(quantize(x)) in x's dtype, in one pass and without a payload:
+// x and out are (out_f, in_f) row-major of `dtype`.  `group` is the NF4 block size or
+// the int4 group size; `scale_dtype` the dtype the int4 / int8 scales would be stored
+// in; `tensor_amax` (NVFP4 only) a device scalar holding max|x|.  Bit-identical to
+// running the format's quantize and dequantize kernels one after the other.
+cudaError_t launch_fake_quant(int format, const void* x, void* out, int dtype, int64_t out_f,
+                              int64_t in_f, int group, int scale_dtype, const float* tensor_amax,
+                              cudaStream_t st);
 
 }  // namespace oab

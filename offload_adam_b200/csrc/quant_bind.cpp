@@ -2,6 +2,8 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <torch/extension.h>
 
+#include <optional>
+
 #include "quant.h"
 
 namespace py = pybind11;
@@ -93,6 +95,18 @@ void int4_dequantize(const Tensor& qweight, const Tensor& scales, int64_t group,
                                  (int)group, out.data_ptr(), cur()), "int4_dequantize");
 }
 
+void fake_quant(int64_t format, const Tensor& x, Tensor out, int64_t group, int64_t scale_dtype, const std::optional<Tensor>& amax) {
+  dense(x, "x"); dense(out, "out");
+  TORCH_CHECK(x.dim() == 2 && out.sizes() == x.sizes() && out.scalar_type() == x.scalar_type(), "fake_quant: out like x (2-D)");
+  const float* ap = nullptr;
+  if (amax.has_value() && amax->defined()) {
+    TORCH_CHECK(amax->is_cuda() && amax->scalar_type() == at::kFloat, "amax: CUDA fp32");
+    ap = amax->data_ptr<float>();
+  }
+  ok(oab::launch_fake_quant((int)format, x.data_ptr(), out.data_ptr(), qdtype(x), x.size(0), x.size(1), (int)group,
+                            (int)scale_dtype, ap, cur()), "fake_quant");
+}
+
 }  // namespace
 
 void bind_quant(py::module_& m) {
@@ -105,4 +119,6 @@ void bind_quant(py::module_& m) {
   m.def("int8_dequantize", &int8_dequantize);
   m.def("int4_quantize", &int4_quantize);
   m.def("int4_dequantize", &int4_dequantize);
+  m.def("fake_quant", &fake_quant, py::arg("format"), py::arg("x"), py::arg("out"), py::arg("group"),
+        py::arg("scale_dtype"), py::arg("amax") = py::none());
 }

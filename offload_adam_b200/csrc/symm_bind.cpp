@@ -27,7 +27,7 @@ int* status_ptr(const Tensor& status) {
 }
 
 void peer_reduce(Tensor out, const std::vector<int64_t>& peers, double scale, const OptT& sumsq,
-                 const OptT& scratch, const OptT& status, int64_t max_ctas, int64_t stream) {
+                 const OptT& scratch, const OptT& status, int64_t max_ctas, int64_t stream, const OptT& acc) {
   TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kBFloat16, "out: contiguous CUDA bf16");
   TORCH_CHECK(!peers.empty() && peers.size() <= (size_t)oab::kMaxPeers, "1..8 peers");
   oab::PeerReduceArgs a;
@@ -36,6 +36,11 @@ void peer_reduce(Tensor out, const std::vector<int64_t>& peers, double scale, co
   a.n_peers = (int)peers.size();
   for (size_t j = 0; j < peers.size(); ++j) a.peers[j] = reinterpret_cast<const void*>(peers[j]);
   a.scale = (float)scale;
+  if (acc.has_value() && acc->defined()) {
+    TORCH_CHECK(acc->is_cuda() && acc->is_contiguous() && acc->scalar_type() == at::kBFloat16 && acc->numel() == out.numel(),
+                "acc: contiguous CUDA bf16 of out's size");
+    a.acc_in = acc->data_ptr();
+  }
   if (sumsq.has_value() && sumsq->defined()) {
     TORCH_CHECK(scratch.has_value() && scratch->defined(), "sumsq needs scratch");
     a.sumsq_out = sumsq->data_ptr<float>();
@@ -64,7 +69,7 @@ void signal(const std::vector<int64_t>& ptrs, int64_t value, int64_t stream) {
 void scalar_exchange(const Tensor& my_value, const std::vector<int64_t>& peer_slots,
                      const std::vector<int64_t>& peer_flags, const Tensor& local_slots,
                      const Tensor& local_flags, int64_t rank, int64_t epoch, double timeout_ms,
-                     const Tensor& status, Tensor out, int64_t stream) {
+                     const Tensor& status, Tensor out, int64_t stream, bool op_max) {
   const size_t n = peer_slots.size();
   TORCH_CHECK(n >= 1 && n <= (size_t)oab::kMaxPeers && peer_flags.size() == n, "1..8 peers");
   TORCH_CHECK(my_value.is_cuda() && out.is_cuda() && local_slots.is_cuda() && local_flags.is_cuda(), "CUDA tensors");
@@ -83,6 +88,7 @@ void scalar_exchange(const Tensor& my_value, const std::vector<int64_t>& peer_sl
   a.timeout_ns = (uint64_t)(timeout_ms * 1e6);
   a.status = status_ptr(status);
   a.out = out.data_ptr<float>();
+  a.op_max = op_max;
   ok(oab::launch_scalar_exchange(a, pick(stream)), "scalar_exchange");
 }
 
@@ -98,13 +104,14 @@ void bind_symm(py::module_& m) {
   m.def("mirror_words", &mirror_words, py::arg("src"), py::arg("dst"), py::arg("stream") = 0);
   m.def("peer_reduce", &peer_reduce, py::arg("out"), py::arg("peers"), py::arg("scale"),
         py::arg("sumsq") = py::none(), py::arg("scratch") = py::none(), py::arg("status") = py::none(),
-        py::arg("max_ctas") = 0, py::arg("stream") = 0);
+        py::arg("max_ctas") = 0, py::arg("stream") = 0, py::arg("acc") = py::none());
   m.def("wait_flags", &wait_flags, py::arg("flags"), py::arg("offset"), py::arg("n"), py::arg("epoch"),
         py::arg("timeout_ms"), py::arg("status"), py::arg("code"), py::arg("stream") = 0);
   m.def("signal", &signal, py::arg("ptrs"), py::arg("value"), py::arg("stream") = 0);
   m.def("scalar_exchange", &scalar_exchange, py::arg("my_value"), py::arg("peer_slots"),
         py::arg("peer_flags"), py::arg("local_slots"), py::arg("local_flags"), py::arg("rank"),
-        py::arg("epoch"), py::arg("timeout_ms"), py::arg("status"), py::arg("out"), py::arg("stream") = 0);
+        py::arg("epoch"), py::arg("timeout_ms"), py::arg("status"), py::arg("out"), py::arg("stream") = 0,
+        py::arg("op_max") = false);
   m.attr("SYMM_TIMEOUT_GRAD") = (int)oab::kSymmTimeoutGrad;
   m.attr("SYMM_TIMEOUT_PARAM") = (int)oab::kSymmTimeoutParam;
   m.attr("SYMM_TIMEOUT_SCALAR") = (int)oab::kSymmTimeoutScalar;

@@ -55,9 +55,12 @@ struct PeerPtrs {
   int n;
 };
 
-template <bool SUMSQ>
+// out = bf16(scale * sum_j peers[j]) or, with `acc`, bf16(acc + that bf16 value): the
+// second form accumulates the mean of one micro-batch into a shard-sized accumulator
+// with the roundings of a reduce-scatter(AVG) followed by an in-place bf16 add.
+template <bool SUMSQ, bool ACC>
 __global__ void __launch_bounds__(kThreads)
-peer_reduce_kernel(uint16_t* out, PeerPtrs pp, int64_t n, float scale, float* sumsq_out,
+peer_reduce_kernel(uint16_t* out, const uint16_t* acc_in, PeerPtrs pp, int64_t n, float scale, float* sumsq_out,
                    float* scratch, int vector_ok, const int* abort_flag) {
   __shared__ float red[kThreads / 32];
   __shared__ int is_last;
@@ -74,6 +77,8 @@ peer_reduce_kernel(uint16_t* out, PeerPtrs pp, int64_t n, float scale, float* su
 #pragma unroll
       for (int j = 0; j < kMaxPeers; ++j)
         if (j < pp.n) in[j] = ld32_peer(pp.g[j] + vec * 16);
+      V8 prev;
+      if (ACC) prev = ld32_stream(acc_in + vec * 16);
       V8 r;
 #pragma unroll
       for (int w = 0; w < 8; ++w) {
@@ -84,8 +89,12 @@ peer_reduce_kernel(uint16_t* out, PeerPtrs pp, int64_t n, float scale, float* su
             lo = __fadd_rn(lo, __uint_as_float(in[j].w[w] << 16));
             hi = __fadd_rn(hi, __uint_as_float(in[j].w[w] & 0xffff0000u));
           }
-        const uint32_t blo = f32_to_bf16_rne_bits(__fmul_rn(lo, scale));
-        const uint32_t bhi = f32_to_bf16_rne_bits(__fmul_rn(hi, scale));
+        uint32_t blo = f32_to_bf16_rne_bits(__fmul_rn(lo, scale));
+        uint32_t bhi = f32_to_bf16_rne_bits(__fmul_rn(hi, scale));
+        if (ACC) {
+          blo = f32_to_bf16_rne_bits(__fadd_rn(__uint_as_float(prev.w[w] << 16), __uint_as_float(blo << 16)));
+          bhi = f32_to_bf16_rne_bits(__fadd_rn(__uint_as_float(prev.w[w] & 0xffff0000u), __uint_as_float(bhi << 16)));
+        }
         r.w[w] = blo | (bhi << 16);
         if (SUMSQ) {
           const float flo = __uint_as_float(blo << 16), fhi = __uint_as_float(bhi << 16);
@@ -99,7 +108,8 @@ peer_reduce_kernel(uint16_t* out, PeerPtrs pp, int64_t n, float scale, float* su
   for (int64_t i = scalar_begin + tid; i < n; i += nthreads) {
     float s = 0.f;
     for (int j = 0; j < pp.n; ++j) s = __fadd_rn(s, bf16_bits_to_f32(pp.g[j][i]));
-    const uint32_t b = f32_to_bf16_rne_bits(__fmul_rn(s, scale));
+    uint32_t b = f32_to_bf16_rne_bits(__fmul_rn(s, scale));
+    if (ACC) b = f32_to_bf16_rne_bits(__fadd_rn(bf16_bits_to_f32(acc_in[i]), bf16_bits_to_f32(b)));
     out[i] = (uint16_t)b;
     if (SUMSQ) { const float f = bf16_bits_to_f32(b); acc = __fadd_rn(acc, __fmul_rn(f, f)); }
   }
@@ -140,7 +150,7 @@ struct ExchangePtrs {
 };
 __global__ void scalar_exchange_kernel(const float* my_value, ExchangePtrs ep, const float* local_slots,
                                        const uint32_t* local_flags, int n, int rank, uint32_t epoch,
-                                       uint64_t timeout_ns, int* status, float* out) {
+                                       uint64_t timeout_ns, int* status, float* out, int op_max) {
   if (*reinterpret_cast<volatile int*>(status) != 0) return;
   const int j = threadIdx.x;
   const uint64_t t0 = global_timer_ns();
@@ -162,7 +172,10 @@ __global__ void scalar_exchange_kernel(const float* my_value, ExchangePtrs ep, c
       return;
     }
     float s = 0.f;
-    for (int k = 0; k < n; ++k) s = __fadd_rn(s, *reinterpret_cast<const volatile float*>(local_slots + k));
+    for (int k = 0; k < n; ++k) {
+      const float x = *reinterpret_cast<const volatile float*>(local_slots + k);
+      s = op_max ? fmaxf(s, x) : __fadd_rn(s, x);
+    }
     *out = s;
   }
 }
@@ -186,12 +199,15 @@ cudaError_t launch_peer_reduce(const PeerReduceArgs& a, cudaStream_t stream) {
   int cap = a.max_ctas > 0 ? (a.max_ctas < kMaxPartials ? a.max_ctas : kMaxPartials) : kMaxPartials;
   int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
   count_launch();
-  if (a.sumsq_out)
-    peer_reduce_kernel<true><<<grid, kThreads, 0, stream>>>((uint16_t*)a.out, pp, a.n, a.scale, a.sumsq_out,
-                                                          a.scratch, vector_ok, a.abort_flag);
-  else
-    peer_reduce_kernel<false><<<grid, kThreads, 0, stream>>>((uint16_t*)a.out, pp, a.n, a.scale, nullptr,
-                                                           nullptr, vector_ok, a.abort_flag);
+  const uint16_t* acc = (const uint16_t*)a.acc_in;
+  if (acc != nullptr) vector_ok = vector_ok && al(acc);
+#define OAB_PR(SQ, AC)                                                                              \
+  peer_reduce_kernel<SQ, AC><<<grid, kThreads, 0, stream>>>((uint16_t*)a.out, acc, pp, a.n, a.scale,    \
+                                                            (SQ) ? a.sumsq_out : nullptr,               \
+                                                            (SQ) ? a.scratch : nullptr, vector_ok, a.abort_flag)
+  if (a.sumsq_out) { if (acc) OAB_PR(true, true); else OAB_PR(true, false); }
+  else { if (acc) OAB_PR(false, true); else OAB_PR(false, false); }
+#undef OAB_PR
   return cudaGetLastError();
 }
 
@@ -231,7 +247,7 @@ cudaError_t launch_scalar_exchange(const ScalarExchangeArgs& a, cudaStream_t str
   }
   count_launch();
   scalar_exchange_kernel<<<1, 32, 0, stream>>>(a.my_value, ep, a.local_slots, a.local_flags, a.n, a.rank,
-                                               a.epoch, a.timeout_ns, a.status, a.out);
+                                               a.epoch, a.timeout_ns, a.status, a.out, a.op_max ? 1 : 0);
   return cudaGetLastError();
 }
 

@@ -22,6 +22,9 @@ enum SymmStatus : int {
 // device.  Returns without touching memory when *abort_flag != 0.
 struct PeerReduceArgs {
   void* out = nullptr;
+  // optional: out = bf16(acc_in + bf16(scale * sum)) (acc_in may alias out): one micro-batch's
+  // mean added to an accumulator, rounded like reduce-scatter(AVG) + in-place bf16 add
+  const void* acc_in = nullptr;
   const void* peers[kMaxPeers] = {};
   int n_peers = 0;
   int64_t n = 0;
@@ -47,9 +50,11 @@ cudaError_t launch_signal(uint32_t* const* ptrs_host, int n, uint32_t value, cud
 // mirrored into mapped host memory without queueing behind bulk DMA copies.
 cudaError_t launch_mirror_words(const int* src, int* dst, int n, cudaStream_t stream);
 
-// Single-kernel all-reduce(SUM) of one fp32 scalar across ranks: stores *my_value into
-// slot[rank] of every peer, raises flag[rank] there, waits (bounded) for all local
-// flags and writes the rank-ordered sum to *out.
+// Single-kernel all-reduce of one fp32 scalar across ranks (SUM in rank order, or MAX of
+// non-negative values): stores *my_value into slot[rank] of every peer, raises
+// flag[rank] there, waits (bounded) for all local flags and writes the result to *out.
+// Consecutive exchanges must alternate between two sets of slots and flags and use
+// increasing epochs: a rank can be one exchange ahead of the slowest one, never two.
 struct ScalarExchangeArgs {
   const float* my_value = nullptr;
   float* peer_slots[kMaxPeers] = {};     // base of each rank's slot array (n floats)
@@ -62,6 +67,7 @@ struct ScalarExchangeArgs {
   uint64_t timeout_ns = 0;
   int* status = nullptr;
   float* out = nullptr;
+  bool op_max = false;
 };
 cudaError_t launch_scalar_exchange(const ScalarExchangeArgs& a, cudaStream_t stream);
 

@@ -64,6 +64,7 @@ class TransferEngine:
         self._marks, self._last_marks = [], []
         self.scratch = None
         self.staging_bytes = 0
+        self._ring_floor_extra = 0
         if self.cuda:
             self.C = _ext.load(required=True)
             with torch.cuda.device(self.device):
@@ -80,6 +81,7 @@ class TransferEngine:
                     # prefetched, the chunks loaded during the step still find room
                     nbytes = max(int(ring_slots) * chunk_elems * 10, int(staging_bytes)) + floor
                     self.chunk_elems = chunk_elems
+                    self._ring_floor_extra = int(ring_slots) * chunk_elems * 10
                     nbytes = (nbytes + 255) // 256 * 256
                     smallest = (max(int(ring_slots) * chunk_elems * 10, floor) + 255) // 256 * 256
                     while True:
@@ -150,12 +152,13 @@ class TransferEngine:
 
     def start_prefetch(self, items, max_inflight=2):
         """Hand a plan of early loads to the engine's helper thread: ``items`` is a list
-        of ``(pid, states)`` in the order the tensors will be stepped.  The thread keeps
+        of ``(pid, states, chunk)`` in the order the tensors will be stepped (``chunk``: the
+        tensor's own chunk length in elements, 0 for the engine's).  The thread keeps
         ``max_inflight`` chunk copies outstanding until the staging buffer is full."""
         if self._native is None or not items:
             return
-        plan = [(pid, st["exp_avg"], st["exp_avg_sq"], st.get("master_params", st.get("rounding_error")))
-                for pid, st in items]
+        plan = [(pid, st["exp_avg"], st["exp_avg_sq"], st.get("master_params", st.get("rounding_error")),
+                 int(chunk)) for pid, st, chunk in items]
         self._native.start_prefetch(self.mode_id, plan, int(max_inflight))
 
     def wait_writeback(self):
@@ -183,7 +186,47 @@ class TransferEngine:
     def can_prefetch(self):
         return self._native is not None and not self.serialize
 
-    def prefetch(self, pid, states, host_grad=None, from_off=0, max_chunks=0, max_inflight=0):
+    def make_resident(self, pid, n):
+        """Give tensor ``pid`` (``n`` elements of state) a permanent place at the front of
+        the staging buffer: loaded once, stepped with one launch, written back after
+        every step, never loaded again.  Only before the first step or early load.
+        Returns False when it does not fit."""
+        if self._native is None:
+            return False
+        return bool(self._native.make_resident(int(pid), self.mode_id, int(n)))
+
+    @property
+    def can_make_resident(self):
+        return self._native is not None
+
+    def resident_budget(self, state_bytes):
+        """Bytes of the staging buffer that resident tensors may take when the optimizer's
+        state is ``state_bytes`` in all: everything when it fits next to the smallest
+        ring, else all but a ring of an eighth of the buffer (at most 4 GiB), through
+        which the other tensors stream."""
+        if self._native is None:
+            return 0
+        floor = self.C.OffloadEngine.min_ring_bytes(self.chunk_elems) + self._ring_floor_extra
+        have = self.staging_bytes
+        if state_bytes + floor <= have:
+            return have - floor
+        ring = max(floor, min(4 << 30, have // 8))
+        return max(0, have - ring)
+
+    def wait_host_grad(self, pid):
+        """Order later work of the optimizer stream after the last copy of tensor ``pid``'s
+        gradient into its host buffer (callers whose kernels read that buffer directly)."""
+        if self._native is not None:
+            self._native.wait_host_grad(int(pid))
+
+    def is_resident(self, pid):
+        return self._native is not None and self._native.is_resident(int(pid))
+
+    @property
+    def resident_bytes(self):
+        return int(self._native.resident_bytes()) if self._native is not None else 0
+
+    def prefetch(self, pid, states, host_grad=None, from_off=0, max_chunks=0, max_inflight=0, chunk=0):
         """Start the H2D of a tensor's state ahead of its step (staged transfer only),
         at most ``max_chunks`` chunks of it (0: as many as fit).  Returns
         ``(offset, full)``: the element offset up to which the tensor is loaded and
@@ -195,7 +238,7 @@ class TransferEngine:
         extra = states.get("master_params", states.get("rounding_error"))
         return self._native.prefetch(pid, self.mode_id, host_grad, states["exp_avg"],
                                      states["exp_avg_sq"], extra, int(from_off), int(max_chunks),
-                                     int(max_inflight))
+                                     int(max_inflight), int(chunk))
 
     def synchronize(self):
         """Block the host until everything enqueued so far has finished, including
@@ -256,7 +299,8 @@ class TransferEngine:
 
     # ------------------------------------------------------------------- step
     def step(self, pid, param, dev_grad, host_grad, states, hp, step, decoupled, clip=None, seed=0,
-             amax=None, fork=True, g_peers=None, g_scale=1.0, p_peers=None, status=None):
+             amax=None, fork=True, g_peers=None, g_scale=1.0, p_peers=None, status=None, quant=None,
+             chunk=0, master_copy=None):
         """Adam step of one offloaded tensor (or shard).
 
         ``states`` holds the host tensors ``exp_avg``, ``exp_avg_sq`` and, by mode,
@@ -266,19 +310,30 @@ class TransferEngine:
         pulled over NVLink.  ``p_peers`` makes the kernel store the updated bf16 rows
         into every replica.  ``param`` may be None when no bf16 write-back is wanted
         (fp32_master only).
+
+        ``quant`` (a ``_C.QuantSpec``; staged transfer only) re-quantizes the updated
+        master and stores the packed rows into every replica named by the spec in the same
+        pass; ``chunk`` is then the tensor's chunk length (whole rows).  For NVFP4, whose
+        tensor scale needs the whole updated weight, the pass only leaves max|master| in
+        ``amax`` and the updated master on the device (in ``master_copy`` unless the tensor
+        is resident); the address to quantize from is returned.
         """
         lr, wd, beta1, beta2, eps = hp
         if self.cuda and fork:
             self.fork_from_main()
         if self._native is not None:
             extra = states.get("master_params", states.get("rounding_error"))
-            self._native.staged_step(
+            where = self._native.staged_step(
                 pid, self.mode_id, param, dev_grad, host_grad, states["exp_avg"],
                 states["exp_avg_sq"], extra, float(lr), float(wd), beta_hat(beta1, step),
                 beta_hat(beta2, step), float(eps), bool(decoupled), clip, int(seed), 0, amax,
-                list(g_peers or ()), float(g_scale), list(p_peers or ()), status,
+                list(g_peers or ()), float(g_scale), list(p_peers or ()), status, int(chunk), quant,
+                master_copy,
             )
         else:
+            if quant is not None:
+                raise RuntimeError("fused re-quantization needs transfer='staged'")
+            where = 0
             st = dict(states)
             if dev_grad is not None:
                 st["grad"], g2 = dev_grad, host_grad
@@ -294,6 +349,7 @@ class TransferEngine:
         self._retain(dev_grad)
         if self.serialize:
             self.synchronize()
+        return where
 
     def bytes_moved(self):
         if self._native is not None:

@@ -82,12 +82,16 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         decoupled_weight_decay: AdamW-style decay.
         inplace_param_threshold: parameters with fewer elements keep state and
             gradient on the GPU (default 1 Mi elements; 0 offloads everything).
-        prefetch_policy: ``'eager'`` or ``'lazy'``: which owner module of a
-            parameter may trigger early work for it.  With the streaming
-            transfer modes of this implementation state is never parked on the
-            GPU ahead of its step, so tied parameters cost no extra residency
-            under either policy; the argument is validated and kept for
-            interface compatibility.
+        prefetch_policy: ``'eager'`` or ``'lazy'``.  In the reference the policy decides
+            which owner module of a shared (tied) parameter brings its state to the GPU
+            ahead of the step, and how long that state stays there.  Here state is
+            streamed through a staging buffer in the order of the steps, so the policy
+            only decides where a shared parameter sits in the early-load order of the
+            step-in-backward path before that order has been observed: ``'eager'`` places
+            it where its last owner module sits (the first one backward reaches),
+            ``'lazy'`` where its first owner sits (the input side, reached last).  From
+            the second step on the observed order is used under both policies, and the
+            clipping path always steps in parameter order.
         verbose: non-zero prints allocation summaries.
         transfer: ``'auto'`` | ``'zero_copy'`` | ``'staged'`` (see module doc).
         grad_residency: ``'auto'`` | ``'host'`` | ``'device'``.
@@ -121,6 +125,13 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             (default): this rank's state size, at most a quarter of the device's memory
             and a third of the memory that is free when the optimizer is built.  A few hundred MB are
             enough for the step itself; everything above that buys overlap.
+        keep_resident: let state that fits in the staging buffer stay there between
+            steps (default).  Such tensors are loaded once, stepped with one launch and
+            written back to the host after every step, so the host copy stays current and
+            authoritative while nothing crosses the host link towards the GPU for them.
+            When the buffer cannot hold everything, the tensors that are stepped last
+            stay and the others stream through the rest of the buffer.  ``False``
+            streams everything every step.
         max_ctas: grid cap of the streaming kernels (0: kernel default); small
             values leave the SMs to the concurrent backward GEMMs.
         seed: seeds the stochastic-rounding stream.
@@ -150,7 +161,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                  prefetch_policy="eager", verbose=0, *, transfer="auto", grad_residency="auto",
                  device_grad_budget=None, chunk_elems=None, ring_slots=4, max_ctas=0,
                  max_inflight_bytes=8 << 30, staging_bytes=None, prefetch_inflight=2, prefetch_pacing="thread", async_writeback=True,
-                 debug_serialize=False, nvtx=False, seed=None):
+                 debug_serialize=False, nvtx=False, seed=None, keep_resident=True):
         if prefetch_policy not in ("eager", "lazy"):
             raise ValueError(f"prefetch_policy must be 'eager' or 'lazy' (got {prefetch_policy!r})")
         if grad_residency not in ("auto", "host", "device"):
@@ -170,7 +181,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         self.decoupled_weight_decay = decoupled_weight_decay
         self.verbose = verbose
         self.ready_for_optimizer_step = False
-        self._rng = random.Random(seed)
+        self._rng = random.Random(self._resolve_seed(seed))
+        self.keep_resident = bool(keep_resident)
 
         # ---- collect parameters: unique by identity, count owning leaf modules
         modules = get_leaf_modules_with_params(model)
@@ -225,12 +237,17 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             raise ValueError(f"{type(self).__name__} expects bfloat16 parameters (found {sorted(not_bf16)}); "
                              "call model.to(torch.bfloat16) first")
 
-        # first owner module in forward order; 'lazy' triggers early work only there
-        self._prefetch_module = {}
-        for m in modules:
+        # position (in forward order) of the owner module that stands for a parameter in
+        # the first guess of the backward order: the first owner under 'lazy', the last
+        # under 'eager' (they differ for shared parameters only)
+        self._owner_pos = {}
+        for pos, m in enumerate(modules):
             for p in m.parameters(recurse=False):
                 if p.requires_grad and p not in self._inplace_params:
-                    self._prefetch_module.setdefault(p, m)
+                    if prefetch_policy == "lazy":
+                        self._owner_pos.setdefault(p, pos)
+                    else:
+                        self._owner_pos[p] = pos
 
         # ---- where gradient accumulators live
         grad_bytes = self._grad_accumulator_bytes()
@@ -275,11 +292,61 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         # main-stream reductions get their own scratch: the engine's belongs to its side stream
         self._scratch_main = grad_ops.sumsq_scratch(self.device)
 
+        self._fused_quant = {}   # quantized param -> dict(chunk, spec) or None (unfused route)
+        self._master_tmp = None  # device copy of an updated NVFP4 master between its two passes
+        self._amax = None
         self._register_hooks(model, modules, params)
         self._numa_precheck(self._offload_params, numa_node)
         self._alloc_pinned_states(self._offload_params, numa_node)
         self._alloc_inplace_states(self._inplace_params)
+        self._choose_resident()
         self._constructed = True
+
+    def _resolve_seed(self, seed):
+        """Seed of the stochastic-rounding stream.  ``None`` draws from Python's global
+        ``random`` module, so that ``random.seed(...)`` makes runs repeatable as it does
+        for the reference (reference: src/offload_adam/kernels/stochastic_rounding.py:98-99)."""
+        return random.getrandbits(63) if seed is None else seed
+
+    # ------------------------------------------------------- resident state
+    def _step_order_guess(self):
+        """Offloaded parameters in the order their steps are expected: parameter order
+        on the clipping path; on the step-in-backward path the order observed in the
+        previous step or, before there is one, owner modules from the output side
+        back to the input side."""
+        if not self._step_in_backward:
+            return [p for g in self.param_groups for p in g["params"] if p not in self._inplace_params]
+        if self._hook_order_prev:
+            return list(self._hook_order_prev)
+        pos = self._owner_pos
+        return sorted((p for p in self._offload_params), key=lambda p: -pos.get(p, 0))
+
+    def _state_elems(self, p):
+        return self.state[p]["exp_avg"].numel()
+
+    def _choose_resident(self):
+        """Pick the tensors whose state stays in the staging buffer (see ``keep_resident``).
+        The tail of the step order is taken: the streamed tensors then go first, their
+        write-backs are not queued behind gigabytes of resident state, and the chunks they
+        occupy are free again when the next loads want them."""
+        eng = self._engine
+        self._resident = set()
+        if not (self.keep_resident and self._cuda and eng.can_make_resident and self.grad_residency == "device"):
+            return
+        per_elem = sum(torch.empty(0, dtype=self.offload_config[k]).element_size() for k in self._non_grad_keys)
+        need = {p: self._state_elems(p) * per_elem + 768 for p in self._offload_params}
+        total = sum(need.values())
+        budget = eng.resident_budget(total)
+        for p in reversed(self._step_order_guess()):
+            if need[p] > budget:
+                break
+            if not eng.make_resident(self._pid[p], self._state_elems(p)):
+                break
+            budget -= need[p]
+            self._resident.add(p)
+        if self.verbose > 0 and self._resident:
+            print(f"{self._log_prefix()}state resident in the staging buffer: {len(self._resident)} of "
+                  f"{len(self._offload_params)} tensors, {eng.resident_bytes / 2**30:.2f} GiB")
 
     def add_param_group(self, param_group):
         if getattr(self, "_constructed", False):
@@ -305,8 +372,12 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             else:
                 self._hook_handles.append(p.register_post_accumulate_grad_hook(self._grad_hook))
                 st["host_grad_valid"] = False
-        # the next forward must see every update even if the caller skipped step()
+        # the next forward must see every update even if the caller skipped step(); so must
+        # a state_dict() of the model taken right after backward (steps of the small
+        # parameters are deferred to this point on the step-in-backward path)
         self._hook_handles.append(model.register_forward_pre_hook(lambda *_: self._on_forward()))
+        if hasattr(model, "register_state_dict_pre_hook"):
+            self._hook_handles.append(model.register_state_dict_pre_hook(lambda *_: self._finish_step()))
         # pacing points for the early H2D during forward (plain forward hooks add no
         # autograd nodes); not needed when the helper thread paces
         for m in (modules if self.prefetch_pacing == "hooks" else ()):
@@ -421,12 +492,6 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                   f"{total / 1024**2:.2f} MB")
 
     # ------------------------------------------------------------ hook bodies
-    def _pre_backward_hook(self, module, grad_output):
-        # Streaming transfers need no state parked on the GPU ahead of time; the
-        # hook only records the order in which owner modules are reached, which
-        # diagnostics and the distributed subclass use.
-        return None
-
     def _resolve_staging_bytes(self, staging_bytes):
         state = self._estimate_pinned_bytes(self._offload_params)
         if staging_bytes is None:
@@ -544,10 +609,99 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         st["host_grad_valid"] = False
         self._after_param_update(p)
 
+    # ------------------------------------------------------- quantized weights
+    def _quant_replicas(self, p):
+        """``(row0, payload0 addresses, payload1 addresses)``: which rows of the weight this
+        optimizer updates and where their packed form goes (subclasses add the other
+        ranks' replicas)."""
+        a, b = p.KERNEL_PAYLOAD
+        return 0, [getattr(p, a).data_ptr()], [getattr(p, b).data_ptr()]
+
+    def _fused_quant_ok(self, p):
+        return self._fused_quant_plan(p) is not None
+
+    def _fused_quant_plan(self, p):
+        """How quantized parameter ``p`` is stepped: a dict for the fused route (Adam on the
+        master chunk by chunk through the staging buffer, re-quantization and the store of
+        the packed rows in the same pass) or None for the unfused one (CPU tensors, shapes
+        the kernels do not take, ``transfer='zero_copy'``)."""
+        if p in self._fused_quant:
+            return self._fused_quant[p]
+        plan = None
+        eng = self._engine
+        C = getattr(eng, "C", None)
+        scale_ids = None if C is None else {torch.float32: C.QDT_F32, torch.bfloat16: C.QDT_BF16,
+                                            torch.float16: C.QDT_F16}
+        if (self._cuda and eng._native is not None and p.KERNEL_FORMAT and p.dim() == 2
+                and p.kernel_scale_dtype() in scale_ids
+                and C.adam_quant_supported(p.KERNEL_FORMAT, p.shape[1], p.kernel_group())
+                and all(getattr(p, k).is_contiguous() for k in p.KERNEL_PAYLOAD)):
+            in_f = p.shape[1]
+            rows = max(1, eng.chunk_elems // in_f)
+            if rows >= 32:
+                rows = rows // 32 * 32  # whole 32-row tiles for the transposed int4 payload
+            row0, pay0, pay1 = self._quant_replicas(p)
+            nvfp4 = bool(p.USES_TENSOR_AMAX)
+            if nvfp4 and self._amax is None:
+                self._amax = torch.zeros(2 * len(self._all_params), dtype=torch.float32, device=self.device)
+            i = self._pid[p]
+            local_amax = self._amax[2 * i: 2 * i + 1] if nvfp4 else None
+            tensor_amax = self._amax[2 * i + 1: 2 * i + 2] if (nvfp4 and self._quant_amax_is_global(p)) else local_amax
+            spec = C.QuantSpec(p.KERNEL_FORMAT, p.shape[0], in_f, row0, p.kernel_group(),
+                               scale_ids[p.kernel_scale_dtype()], pay0, pay1, tensor_amax,
+                               p.global_scale if nvfp4 else None)
+            plan = {"chunk": rows * in_f, "spec": spec, "nvfp4": nvfp4, "local_amax": local_amax,
+                    "tensor_amax": tensor_amax}
+        self._fused_quant[p] = plan
+        return plan
+
+    def _quant_amax_is_global(self, p):
+        """True when max|master| of ``p`` has to be combined across ranks first."""
+        return False
+
+    def _chunk_for(self, p):
+        """Chunk length of ``p`` in the staging buffer (0: the engine's default)."""
+        if p not in self._quant_params:
+            return 0
+        plan = self._fused_quant_plan(p)
+        return plan["chunk"] if plan else 0
+
+    def _combine_amax(self, p, plan):
+        """Hook for subclasses: turn the local max|master| into the whole weight's."""
+
     def _step_quant(self, p, group, st, dev_grad, host_grad, clip_coef):
-        """Quantized parameter: the updated fp32 master must be on the device to be
-        re-quantized, so it makes the round trip through a temporary while the
-        moments stream as usual."""
+        """Quantized parameter on the fused route: the fp32 master and the moments stream
+        through the staging buffer like any dense tensor; each chunk is a number of whole
+        rows, and the kernel that updates them also re-quantizes them and stores the packed
+        rows (reference: src/offload_adam/offload_adam.py:421-444 keeps the whole master on
+        the GPU and re-quantizes it with a second kernel)."""
+        plan = self._fused_quant_plan(p)
+        if plan is None:
+            return self._step_quant_unfused(p, group, st, dev_grad, host_grad, clip_coef)
+        eng = self._engine
+        states = {k: st[k] for k in self._non_grad_keys}
+        extra = {k: v for k, v in self._step_extra(p).items() if k != "p_peers"}
+        n = states["exp_avg"].numel()
+        tmp = None
+        if plan["nvfp4"] and not eng.is_resident(self._pid[p]):
+            if self._master_tmp is None or self._master_tmp.numel() < n:
+                need = max(self._state_elems(q) for q in self._quant_params if q.USES_TENSOR_AMAX)
+                self._master_tmp = torch.empty(need, dtype=torch.float32, device=self.device)
+            tmp = self._master_tmp
+        where = eng.step(self._pid[p], None, dev_grad, host_grad, states, self._hp(group), st["step"],
+                         self.decoupled_weight_decay, clip=clip_coef, amax=plan["local_amax"],
+                         quant=plan["spec"], chunk=plan["chunk"], master_copy=tmp, **extra)
+        if plan["nvfp4"]:
+            # second pass: the tensor scale needs max|master| of the whole updated weight
+            self._combine_amax(p, plan)
+            eng.C.nvfp4_quantize_push(plan["spec"], where, n, extra.get("status"), eng.opt_stream.cuda_stream)
+            if eng.serialize:
+                eng.synchronize()
+
+    def _step_quant_unfused(self, p, group, st, dev_grad, host_grad, clip_coef):
+        """Quantized parameter without the fused kernels: the fp32 master makes the round
+        trip through a device temporary and a separate kernel (or, on CPU tensors, the
+        PyTorch restatement) re-quantizes it."""
         eng = self._engine
         if not self._cuda:
             states = {k: st[k] for k in self._non_grad_keys}
@@ -614,17 +768,14 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         eng = self._engine
         if not (self._cuda and eng.can_prefetch and self.grad_residency == "device"):
             return
-        if self._step_in_backward:
-            order = self._hook_order_prev
-        else:
-            order = [p for g in self.param_groups for p in g["params"] if p not in self._inplace_params]
+        order = self._step_order_guess()
         if self.prefetch_pacing == "thread" and self.prefetch_inflight > 0:
             items = []
             for p in order or ():
-                if p in self._quant_params:
+                if p in self._quant_params and self._fused_quant_plan(p) is None:
                     break  # takes its own route through a device temporary
                 st = self.state[p]
-                items.append((self._pid[p], {k: st[k] for k in self._non_grad_keys}))
+                items.append((self._pid[p], {k: st[k] for k in self._non_grad_keys}, self._chunk_for(p)))
             eng.start_prefetch(items, self.prefetch_inflight)
             return
         self._pf_order = order or None
@@ -645,16 +796,17 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                 self._pf_order = None
                 return
             p = order[self._pf_idx]
-            if p in self._quant_params:
+            if p in self._quant_params and self._fused_quant_plan(p) is None:
                 self._pf_order = None  # takes its own route through a device temporary
                 return
             st = self.state[p]
             states = {k: st[k] for k in self._non_grad_keys}
-            off, full = eng.prefetch(self._pid[p], states, None, self._pf_off, budget, max_inflight=inflight)
+            off, full = eng.prefetch(self._pid[p], states, None, self._pf_off, budget, max_inflight=inflight,
+                                     chunk=self._chunk_for(p))
             if full:
                 self._pf_order = None  # no staging space left for this step
                 return
-            issued = -(-(off - self._pf_off) // eng.chunk_elems)
+            issued = -(-(off - self._pf_off) // (self._chunk_for(p) or eng.chunk_elems))
             if off >= states["exp_avg"].numel():
                 self._pf_idx += 1
                 self._pf_off = 0
@@ -857,5 +1009,10 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                                          f"has shape/dtype {tuple(v.shape)}/{v.dtype}, expected "
                                          f"{tuple(dst[k].shape)}/{dst[k].dtype}")
                     dst[k].copy_(v)
+                elif k == "host_grad_valid":
+                    continue  # goes with the gradient buffer, which is not restored
                 else:
                     dst[k] = v
+            if "host_grad_valid" in dst:
+                dst["host_grad_valid"] = False
+        self._dev_grad.clear()

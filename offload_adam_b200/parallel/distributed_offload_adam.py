@@ -16,8 +16,9 @@ Two communication back ends implement those three collectives:
 ``comm='symm'``  the parameters and the gradient accumulators live in symmetric
                  memory; one kernel per parameter pulls the peers' gradient rows
                  over NVLink, averages them, runs Adam on the shard and pushes
-                 the new bf16 rows into every replica (``parallel/symm.py``,
-                 ``csrc/symm_ops.cu``, ``csrc/adam_step.cu``).  No NCCL call on that path.
+                 the new bf16 rows (for a quantized weight: the re-quantized packed
+                 rows) into every replica (``parallel/symm.py``, ``csrc/symm_ops.cu``,
+                 ``csrc/adam_step.cu``, ``csrc/adam_quant.cu``).  No NCCL call on that path.
 ``comm='auto'``  ``symm`` on CUDA with world size > 1 when symmetric memory can
                  be set up, else ``nccl``.
 
@@ -49,7 +50,12 @@ class DistributedOffloadAdam(OffloadAdam):
       what lets a model whose full-shape gradient does not fit next to its weights (70B
       on 8 GPUs) train at all; the price is one reduce-scatter per tensor and
       micro-batch, and a different rounding order (mean over ranks first, then the bf16
-      sum over micro-batches).  Uses the ``torch.distributed`` collectives.
+      sum over micro-batches).  With ``comm='symm'`` the reduce-scatter is a pull out of a
+      two-slot exchange window in symmetric memory (``parallel/symm.py``), with
+      ``comm='nccl'`` a ``reduce_scatter_tensor``.
+
+    With ``seed=None`` rank 0 draws the seed of the stochastic-rounding stream and
+    broadcasts it: replicated tensors are stepped on every rank and must round alike.
     """
 
     def __init__(self, model, *, process_group=None, comm="auto", wait_timeout_ms=30000,
@@ -63,10 +69,6 @@ class DistributedOffloadAdam(OffloadAdam):
             raise ValueError(f"comm must be 'auto', 'nccl' or 'symm' (got {comm!r})")
         if grad_layout not in ("full", "shard"):
             raise ValueError(f"grad_layout must be 'full' or 'shard' (got {grad_layout!r})")
-        if grad_layout == "shard":
-            if comm == "symm":
-                raise ValueError("grad_layout='shard' uses the torch.distributed collectives; pass comm='nccl'")
-            comm = "nccl"
         self.grad_layout = grad_layout
         self._pg = process_group if process_group is not None else dist.group.WORLD
         self._world_size = dist.get_world_size(self._pg)
@@ -132,6 +134,13 @@ class DistributedOffloadAdam(OffloadAdam):
     def _log_prefix(self):
         return f"[rank {self._rank}] "
 
+    def _resolve_seed(self, seed):
+        if seed is not None or self._world_size <= 1:
+            return super()._resolve_seed(seed)
+        box = [super()._resolve_seed(None) if self._rank == 0 else None]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(self._pg, 0), group=self._pg)
+        return box[0]
+
     def _copy_master(self, p, tensor):
         self._engine.invalidate_prefetched()  # a copy loaded ahead of time would be stale
         if p in self._sharded:
@@ -148,15 +157,16 @@ class DistributedOffloadAdam(OffloadAdam):
             return
         if want == "nccl":
             return
-        if want == "auto" and self._quant_params:
-            # quantized weights take the collective route for their gradients and packed
-            # payloads; a step that mixes both routes is only selected on request
+        if self.grad_residency != "device":
+            if want == "symm":
+                raise RuntimeError("comm='symm' needs grad_residency='device'")
             return
         from . import symm
 
         try:
             self._symm = symm.SymmZero1(self, model, timeout_ms=self._wait_timeout_ms)
             self.comm = "symm"
+            self._fused_quant = {}  # payload addresses changed: plans are rebuilt on first use
         except Exception as e:
             if want == "symm":
                 raise
@@ -230,6 +240,9 @@ class DistributedOffloadAdam(OffloadAdam):
             return
         symm = self._symm is not None and self._symm.handles(p)
         if self._world_size > 1 and self._shard_grads(p):
+            self._pace_prefetch(1)
+            if symm:
+                return self._symm.grad_hook_window(p, self.ready_for_optimizer_step)
             return self._shard_grad_hook(p, self.ready_for_optimizer_step)
         if not self.ready_for_optimizer_step or self._world_size <= 1:
             if symm:
@@ -251,6 +264,9 @@ class DistributedOffloadAdam(OffloadAdam):
                                          stream=self._opt_stream_handle())
                 full = acc
             elif st["host_grad_valid"]:
+                # the kernel reads the pinned buffer directly: the copy of the previous
+                # micro-batch into it (D2H stream) has to be complete
+                eng.wait_host_grad(self._pid[p])
                 grad_ops.grad_accumulate(grad, grad, st["grad"], use_cuda=self._cuda,
                                          stream=self._opt_stream_handle())
                 full = grad
@@ -293,6 +309,7 @@ class DistributedOffloadAdam(OffloadAdam):
                 self._dev_grad[p] = total
             elif last:
                 if st["host_grad_valid"]:
+                    eng.wait_host_grad(self._pid[p])  # as above: a zero-copy read of the pinned buffer
                     grad_ops.grad_accumulate(red, red, st["grad"], use_cuda=self._cuda, stream=s)
                     st["host_grad_valid"] = False
                 total = red
@@ -325,25 +342,52 @@ class DistributedOffloadAdam(OffloadAdam):
             return self._symm.after_param_update(p)
         if p not in self._sharded:
             return
+        if p in self._quant_params:
+            return  # handled in _step_quant
         with self._side():
-            if p in self._quant_params:
-                return  # handled in _step_quant
             self._all_gather_rows(p.data, self._shard_slice(p))
 
+    def _fused_quant_ok(self, p):
+        """True when the fused Adam + re-quantize + push kernels take this weight."""
+        eng = self._engine
+        C = getattr(eng, "C", None)
+        return bool(self._cuda and eng._native is not None and p.KERNEL_FORMAT and p.dim() == 2
+                    and p.kernel_scale_dtype() in (torch.float32, torch.bfloat16, torch.float16)
+                    and C.adam_quant_supported(p.KERNEL_FORMAT, p.shape[1], p.kernel_group()))
+
+    def _quant_replicas(self, p):
+        if self._symm is not None and self._symm.handles(p):
+            return self._symm.quant_replicas(p)
+        return super()._quant_replicas(p)
+
+    def _quant_amax_is_global(self, p):
+        return self._symm is not None and self._symm.handles(p) and p in self._sharded
+
+    def _combine_amax(self, p, plan):
+        if self._quant_amax_is_global(p):
+            self._symm.combine_amax(plan["local_amax"], plan["tensor_amax"])
+
+    def _fused_quant_plan(self, p):
+        if p in self._sharded and not (self._symm is not None and self._symm.handles(p)):
+            return None  # rows divided among ranks, no peer mappings: the collective route below
+        return super()._fused_quant_plan(p)
+
     def _step_quant(self, p, group, st, dev_grad, host_grad, clip_coef):
-        if p not in self._sharded:
+        if p not in self._sharded or self._fused_quant_plan(p) is not None:
             return super()._step_quant(p, group, st, dev_grad, host_grad, clip_coef)
-        # sharded quantized parameter: the owner of each row range updates its master
-        # slice, quantizes those rows and the PACKED rows are gathered (at most one byte
-        # per element on the wire instead of four, and no replica re-quantizes rows it
-        # does not own).  The reference gathers the fp32 master and re-quantizes the whole
-        # weight on every rank (src/offload_adam/offload_adam.py:893-921).
+        # sharded quantized parameter over torch.distributed: the owner of each row range
+        # updates its master slice, quantizes those rows and the PACKED rows are gathered
+        # (at most one byte per element on the wire instead of four, and no replica
+        # re-quantizes rows it does not own).  The reference gathers the fp32 master and
+        # re-quantizes the whole weight on every rank
+        # (src/offload_adam/distributed_offload_adam.py:250-262).
         eng = self._engine
         from ..ops.adam_step import adam_step
 
         q = p.data
         lo, hi = self._rows(p)
-        eng.fork_from_main()
+        if self._cuda:
+            eng.fork_from_main()
         with self._side():
             master = st["master_params"].to(self.device, non_blocking=True) if self._cuda \
                 else st["master_params"]

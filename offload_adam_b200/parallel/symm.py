@@ -1,20 +1,22 @@
 """Symmetric-memory (NVLink peer access) implementation of the ZeRO-1 collectives.
 
-Set-up: the bf16 parameters of every sharded tensor and a full-shape bf16 gradient
-accumulator for each of them are placed in two symmetric allocations
-(``torch.distributed._symmetric_memory``: same layout on every rank, every rank's
-copy mapped into every GPU).  A third small allocation holds epoch flags, the
-gradient bucket of the small replicated parameters and the slots of the scalar
-exchange.  The kernels are this package's own (``csrc/adam_step.cu`` PEERS variant,
-``csrc/symm_ops.cu``); ``torch.distributed`` is used for bootstrap only.
+Set-up: the bf16 parameters of every sharded dense tensor, the packed payload tensors of
+every quantized weight and a full-shape bf16 gradient accumulator for each of them are
+placed in symmetric allocations (``torch.distributed._symmetric_memory``: same layout on
+every rank, every rank's copy mapped into every GPU).  A small control allocation holds
+epoch flags, the gradient bucket of the small replicated parameters and the slots of the
+scalar exchanges.  The kernels are this package's own (``csrc/adam_step.cu`` PEERS
+variant, ``csrc/adam_quant.cu``, ``csrc/symm_ops.cu``); ``torch.distributed`` is used for
+bootstrap only.
 
-Per optimizer step (epoch ``e``), for a sharded parameter ``p`` owned row-wise:
+Per optimizer step (epoch ``e``), for a tensor ``p`` whose rows are divided among the ranks:
 
 1. last micro-batch hook, main stream: accumulate into ``p``'s symmetric gradient,
    then store ``e`` into ``grad_flag[p][rank]`` on every rank;
 2. optimizer stream: bounded wait until ``grad_flag[p][*] >= e`` locally, then
    * no clipping: one pass pulls the owned rows from all replicas, averages, runs
-     Adam on the shard and pushes the new bf16 rows into all replicas;
+     Adam on the shard and pushes the new bf16 rows (a quantized weight: the re-quantized
+     packed rows and their scales) into all replicas;
    * clipping: one pass pulls and averages the rows into a local slice and reduces
      its squared norm; ``step()`` exchanges one scalar per rank, then the clip-fused
      Adam pass pushes the rows;
@@ -22,8 +24,26 @@ Per optimizer step (epoch ``e``), for a sharded parameter ``p`` owned row-wise:
 3. before the next forward every rank waits (bounded) for all ``param_flag >= e``:
    all replicas are complete and nobody reads this rank's gradients any more.
 
+An NVFP4 weight needs max|master| of the whole updated weight before it can be
+quantized: the Adam pass leaves the rank's maximum, one more scalar exchange (MAX)
+combines them, and a second pass quantizes the rank's rows and pushes them.
+
+``grad_layout='shard'`` replaces the full-shape accumulators by a two-slot exchange
+window: every micro-batch's gradient of a tensor is copied into a slot, the ranks pull
+and average their rows out of all replicas of the slot and add them to a shard-sized
+accumulator; ready/done flags per slot and rank keep a slot from being overwritten
+before every rank has read it.
+
 Small replicated parameters are averaged in one bucket by the same pull kernel.
+The first micro-batch's gradient is copied into the symmetric accumulator (one 4 B per
+element pass, about 5 ms per step for an 8B model); adopting the autograd tensor
+instead, as the single-GPU path does, would keep a second full-size gradient set alive
+between the first two micro-batches.
 (reference: src/offload_adam/distributed_offload_adam.py:61-104, :182-306)
+
+Side effect of construction: ``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` is set in the process
+environment (unless already set) so that these buffers are plain peer mappings and are
+never bound to an NVLink multicast object.
 """
 
 from __future__ import annotations
@@ -35,10 +55,15 @@ from .. import _ext
 from ..ops import grad_ops
 
 _ALIGN = 256
+_WINDOW_SLOTS = 2
 
 
 def _round_up(x, a):
     return (x + a - 1) // a * a
+
+
+def _nbytes(t):
+    return t.numel() * t.element_size()
 
 
 class SymmZero1:
@@ -61,36 +86,69 @@ class SymmZero1:
             raise RuntimeError("symmetric-memory path needs grad_residency='device'")
         group = opt._pg
         self.group_name = group.group_name
+        self.shard_layout = opt.grad_layout == "shard"
+        N = self.N
 
         # ---- which tensors take this path
         # every offloaded dense tensor: row-sharded ones (pull own rows, push them back) and
         # replicated ones whose leading dimension does not divide (pull everything, every
-        # rank steps its own replica with identical bits)
-        self.params = [p for p in opt._offload_params if p not in opt._quant_params]
+        # rank steps its own replica with identical bits); quantized weights when the fused
+        # Adam + re-quantize + push kernels take their shape
+        self.params = [p for p in opt._offload_params
+                       if p not in opt._quant_params or opt._fused_quant_ok(p)]
+        self.is_quant = {p: p in opt._quant_params for p in self.params}
         self.is_sharded = {p: p in opt._sharded for p in self.params}
         self.index = {p: i for i, p in enumerate(self.params)}
         self.small = list(opt._inplace_entries)
         n_sym = len(self.params)
 
         # ---- layouts (identical on every rank)
-        self.off = {}
-        total = 0
+        # gradient arena: a full-shape bf16 accumulator per tensor ('shard' layout: only
+        # for the tensors whose rows do not divide, the others go through the window)
+        self.goff, gtotal = {}, 0
         for p in self.params:
-            self.off[p] = total
-            total += _round_up(p.numel() * 2, _ALIGN)
-        self.arena_bytes = max(total, _ALIGN)
+            if self.shard_layout and self.is_sharded[p]:
+                continue
+            self.goff[p] = gtotal
+            gtotal += _round_up(p.numel() * 2, _ALIGN)
+        # parameter arena: bf16 data of dense tensors, both payload tensors of quantized ones
+        self.poff, ptotal = {}, 0
+        for p in self.params:
+            if self.is_quant[p]:
+                offs = []
+                for name in p.KERNEL_PAYLOAD:
+                    offs.append(ptotal)
+                    ptotal += _round_up(_nbytes(getattr(p, name)), _ALIGN)
+                self.poff[p] = tuple(offs)
+            else:
+                self.poff[p] = ptotal
+                ptotal += _round_up(p.numel() * 2, _ALIGN)
+        self.window_bytes = 0
+        if self.shard_layout:
+            biggest = max((p.numel() * 2 for p in self.params if self.is_sharded[p]), default=0)
+            self.window_bytes = _round_up(biggest, _ALIGN)
         small_off, stotal = [], 0
         for e in self.small:
             small_off.append(stotal)
             stotal += _round_up(e["p"].numel() * 2, 32)
         self.small_bytes = max(stotal, 32)
-        n_flags = 2 * n_sym * self.N + 4 * self.N
+        # flag regions (in words)
+        self.F_GRAD = 0
+        self.F_PARAM = n_sym * N
+        self.F_SMALL_READY = 2 * n_sym * N
+        self.F_SMALL_DONE = self.F_SMALL_READY + N
+        self.F_SCALAR = self.F_SMALL_DONE + N          # 4 sets of N: {main, optimizer stream} x {even, odd}
+        self.F_WIN_READY = self.F_SCALAR + 4 * N       # per window slot and rank
+        self.F_WIN_DONE = self.F_WIN_READY + _WINDOW_SLOTS * N
+        n_flags = self.F_WIN_DONE + _WINDOW_SLOTS * N
         self.ctrl_flag_words = _round_up(n_flags, 64)
-        ctrl_bytes = self.ctrl_flag_words * 4 + _round_up(self.N * 4, _ALIGN) + self.small_bytes
+        self.slots_off = self.ctrl_flag_words * 4
+        self.small_off_bytes = self.slots_off + _round_up(4 * N * 4, _ALIGN)
+        ctrl_bytes = self.small_off_bytes + self.small_bytes
 
         # ---- symmetric allocations + rendezvous
-        self.param_arena = symm_mem.empty(self.arena_bytes, dtype=torch.uint8, device=self.dev)
-        self.grad_arena = symm_mem.empty(self.arena_bytes, dtype=torch.uint8, device=self.dev)
+        self.param_arena = symm_mem.empty(max(ptotal, _ALIGN), dtype=torch.uint8, device=self.dev)
+        self.grad_arena = symm_mem.empty(max(gtotal, _ALIGN), dtype=torch.uint8, device=self.dev)
         self.ctrl = symm_mem.empty(ctrl_bytes, dtype=torch.uint8, device=self.dev)
         self.ctrl.zero_()
         self.grad_arena.zero_()
@@ -100,38 +158,44 @@ class SymmZero1:
         self.param_base = [int(x) for x in self.h_param.buffer_ptrs]
         self.grad_base = [int(x) for x in self.h_grad.buffer_ptrs]
         self.ctrl_base = [int(x) for x in self.h_ctrl.buffer_ptrs]
+        self.window = None
+        if self.window_bytes:
+            self.window = symm_mem.empty(_WINDOW_SLOTS * self.window_bytes, dtype=torch.uint8, device=self.dev)
+            self.h_window = symm_mem.rendezvous(self.window, group)
+            self.window_base = [int(x) for x in self.h_window.buffer_ptrs]
+        self.window_use = 0
 
         # ---- views
         self.flags = self.ctrl[: self.ctrl_flag_words * 4].view(torch.int32)
-        slots_off = self.ctrl_flag_words * 4
-        self.slots = self.ctrl[slots_off: slots_off + self.N * 4].view(torch.float32)
-        self.slots_off = slots_off
-        self.small_off_bytes = slots_off + _round_up(self.N * 4, _ALIGN)
+        self.slots = self.ctrl[self.slots_off: self.slots_off + 4 * N * 4].view(torch.float32)
         self.small_sym = self.ctrl[self.small_off_bytes: self.small_off_bytes + self.small_bytes].view(torch.bfloat16)
-        # flag regions (in words)
-        self.F_GRAD = 0
-        self.F_PARAM = n_sym * self.N
-        self.F_SMALL_READY = 2 * n_sym * self.N
-        self.F_SMALL_DONE = self.F_SMALL_READY + self.N
-        self.F_SCALAR = self.F_SMALL_DONE + self.N
 
-        # ---- move parameters into the symmetric arena, carve gradient views
+        # ---- move parameters (payloads) into the symmetric arena, carve gradient views
         self.grad_view = {}
         for p in self.params:
-            o, n = self.off[p], p.numel()
-            home = self.param_arena[o: o + n * 2].view(torch.bfloat16).view(p.shape)
-            home.copy_(p.data)
-            p.data = home
-            self.grad_view[p] = self.grad_arena[o: o + n * 2].view(torch.bfloat16).view(p.shape)
+            if self.is_quant[p]:
+                for name, o in zip(p.KERNEL_PAYLOAD, self.poff[p]):
+                    t = getattr(p, name)
+                    home = self.param_arena[o: o + _nbytes(t)].view(t.dtype).view(t.shape)
+                    home.copy_(t)
+                    setattr(p, name, home)  # p.data is rebuilt from these attributes on every access
+            else:
+                o, n = self.poff[p], p.numel()
+                home = self.param_arena[o: o + n * 2].view(torch.bfloat16).view(p.shape)
+                home.copy_(p.data)
+                p.data = home
+            if p in self.goff:
+                o, n = self.goff[p], p.numel()
+                self.grad_view[p] = self.grad_arena[o: o + n * 2].view(torch.bfloat16).view(p.shape)
         self.acc_valid = {p: False for p in self.params}
         torch.cuda.empty_cache()  # the parameters' old storage goes back to the driver
-        self.shard_bytes = {p: (p.numel() // self.N if self.is_sharded[p] else p.numel()) * 2
-                            for p in self.params}
-        # reduced gradient slices (clip path keeps them until step())
+        self.shard_bytes = {p: (p.numel() // N if self.is_sharded[p] else p.numel()) * 2 for p in self.params}
+        # reduced gradient slices: the clip path keeps them until step(), the 'shard' layout
+        # accumulates the micro-batches in them
         self.red = {}
-        if opt.max_grad_norm is not None:
-            for p in self.params:
-                shape = (p.shape[0] // self.N, *p.shape[1:]) if self.is_sharded[p] else p.shape
+        for p in self.params:
+            if opt.max_grad_norm is not None or (self.shard_layout and self.is_sharded[p]):
+                shape = (p.shape[0] // N, *p.shape[1:]) if self.is_sharded[p] else tuple(p.shape)
                 self.red[p] = torch.empty(shape, dtype=torch.bfloat16, device=self.dev)
 
         # ---- small replicated parameters: accumulate in symmetric memory, step from a
@@ -156,6 +220,8 @@ class SymmZero1:
         self.local_sq = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.total_sq = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.epoch = 1
+        self.xseq = [1, 1]   # sequence numbers of the scalar exchanges: main stream, optimizer stream
+        self._signaled = set()
         # norm slots counted by this rank: its slices of sharded tensors, plus (rank 0
         # only) everything that is identical on all ranks
         idx = [opt._pid[p] for p in opt._all_params
@@ -169,16 +235,26 @@ class SymmZero1:
         """Address of flag ``word`` of ``region`` in every rank's control block."""
         return [b + 4 * (region + word) for b in self.ctrl_base]
 
-    def _my_rows(self, base, p):
+    def _my_rows(self, base, off, p):
         """Address, in every rank's arena, of the part of ``p`` this rank reduces/updates."""
         first = self.rank * self.shard_bytes[p] if self.is_sharded[p] else 0
-        return [b + self.off[p] + first for b in base]
+        return [b + off + first for b in base]
 
     def handles(self, p):
         return p in self.index
 
     def _opt_stream(self):
         return self.opt._engine.opt_stream.cuda_stream
+
+    def quant_replicas(self, p):
+        """``(row0, payload0 addresses, payload1 addresses)`` of quantized weight ``p``: this
+        rank's first row and the base of both payload tensors in every replica it stores
+        into (all ranks' when the rows are divided, its own otherwise)."""
+        o0, o1 = self.poff[p]
+        if self.is_sharded[p]:
+            row0 = self.rank * (p.shape[0] // self.N)
+            return row0, [b + o0 for b in self.param_base], [b + o1 for b in self.param_base]
+        return 0, [self.param_base[self.rank] + o0], [self.param_base[self.rank] + o1]
 
     # ------------------------------------------------------------------ hooks
     def accumulate(self, p, grad, sumsq=None):
@@ -189,6 +265,43 @@ class SymmZero1:
         else:
             acc.copy_(grad)
             self.acc_valid[p] = True
+
+    def windowed(self, p):
+        return self.shard_layout and self.is_sharded[p]
+
+    @torch.no_grad()
+    def grad_hook_window(self, p, last):
+        """``grad_layout='shard'``: this micro-batch's gradient goes through the exchange
+        window; the mean of this rank's rows over the ranks is added to its shard-sized
+        accumulator."""
+        opt, C, N = self.opt, self.C, self.N
+        grad = opt._take_grad(p)
+        u = self.window_use
+        self.window_use += 1
+        slot = u % _WINDOW_SLOTS
+        if u >= _WINDOW_SLOTS:
+            # every rank has finished reading what this slot held before
+            C.wait_flags(self.flags, self.F_WIN_DONE + slot * N, N, u - _WINDOW_SLOTS + 1, self.timeout_ms,
+                         self.status, C.SYMM_TIMEOUT_GRAD)
+        nbytes = p.numel() * 2
+        off = slot * self.window_bytes
+        self.window[off: off + nbytes].view(torch.bfloat16).view(p.shape).copy_(grad)
+        C.signal(self._flag_ptrs(self.F_WIN_READY, slot * N + self.rank), u + 1)
+        eng = opt._engine
+        eng.fork_from_main()
+        s = self._opt_stream()
+        C.wait_flags(self.flags, self.F_WIN_READY + slot * N, N, u + 1, self.timeout_ms, self.status,
+                     C.SYMM_TIMEOUT_GRAD, s)
+        red = self.red[p]
+        first = opt._dev_grad.get(p) is None
+        want_sq = last and opt.max_grad_norm is not None
+        C.peer_reduce(red, [b + off + self.rank * self.shard_bytes[p] for b in self.window_base], 1.0 / N,
+                      opt._slot(p) if want_sq else None, eng.scratch if want_sq else None, self.status,
+                      eng.max_ctas, s, None if first else red)
+        C.signal(self._flag_ptrs(self.F_WIN_DONE, slot * N + self.rank), u + 1, s)
+        opt._dev_grad[p] = red
+        if last and opt._step_in_backward:
+            opt._step_offload(p, opt._param2group[p])
 
     @torch.no_grad()
     def grad_hook_last(self, p):
@@ -207,22 +320,42 @@ class SymmZero1:
         if opt._step_in_backward:
             opt._step_offload(p, opt._param2group[p])
         else:
-            C.peer_reduce(self.red[p], self._my_rows(self.grad_base, p), 1.0 / N, opt._slot(p),
+            C.peer_reduce(self.red[p], self._my_rows(self.grad_base, self.goff[p], p), 1.0 / N, opt._slot(p),
                           eng.scratch, self.status, eng.max_ctas, s)
             opt._dev_grad[p] = self.red[p]
 
     def step_extra(self, p):
-        """Extra arguments of the Adam pass of a sharded tensor."""
+        """Extra arguments of the Adam pass of a tensor on this path."""
         kw = {"status": self.status}
-        if self.is_sharded[p]:
-            kw["p_peers"] = self._my_rows(self.param_base, p)
-        if self.opt._step_in_backward:
-            kw.update(g_peers=self._my_rows(self.grad_base, p), g_scale=1.0 / self.N)
+        if self.is_sharded[p] and not self.is_quant[p]:
+            kw["p_peers"] = self._my_rows(self.param_base, self.poff[p], p)
+        if self.opt._step_in_backward and not self.windowed(p):
+            kw.update(g_peers=self._my_rows(self.grad_base, self.goff[p], p), g_scale=1.0 / self.N)
         return kw
 
     def after_param_update(self, p):
         i = self.index[p]
+        self._signaled.add(p)
         self.C.signal(self._flag_ptrs(self.F_PARAM, i * self.N + self.rank), self.epoch, self._opt_stream())
+
+    # ------------------------------------------------------------ scalar exchanges
+    def _exchange(self, value, out, on_opt_stream, op_max):
+        """All-reduce of one fp32 scalar through the flag slots.  Exchanges of one stream
+        alternate between two sets of slots and carry increasing sequence numbers."""
+        which = 1 if on_opt_stream else 0
+        k = self.xseq[which]
+        self.xseq[which] = k + 1
+        s = 2 * which + (k & 1)
+        N = self.N
+        self.C.scalar_exchange(value, [b + self.slots_off + 4 * s * N for b in self.ctrl_base],
+                               self._flag_ptrs(self.F_SCALAR, s * N), self.slots[s * N: (s + 1) * N],
+                               self.flags[self.F_SCALAR + s * N: self.F_SCALAR + (s + 1) * N], self.rank, k,
+                               self.timeout_ms, self.status, out,
+                               self._opt_stream() if on_opt_stream else 0, op_max)
+
+    def combine_amax(self, local_amax, tensor_amax):
+        """max|master| of a row-divided NVFP4 weight over all ranks (optimizer stream)."""
+        self._exchange(local_amax, tensor_amax, True, True)
 
     # ------------------------------------------------------------ small bucket
     def reduce_small_bucket(self):
@@ -242,16 +375,13 @@ class SymmZero1:
 
     # -------------------------------------------------------------- clip path
     def global_clip_coef(self):
-        opt, C = self.opt, self.C
+        opt = self.opt
         self.reduce_small_bucket()
         opt._engine.join_main(wait_writeback=False)  # slice norms come from kernels on the optimizer stream
         extra = self.small_sq if (self.rank == 0 and self.small) else None
         grad_ops.clip_finalize(opt._normsq if self.norm_index is not None else None, self.norm_index,
                                extra, opt.max_grad_norm, total_sq=self.local_sq)
-        C.scalar_exchange(self.local_sq, [b + self.slots_off for b in self.ctrl_base],
-                          self._flag_ptrs(self.F_SCALAR, 0), self.slots,
-                          self.flags[self.F_SCALAR: self.F_SCALAR + self.N], self.rank, self.epoch,
-                          self.timeout_ms, self.status, self.total_sq)
+        self._exchange(self.local_sq, self.total_sq, False, False)
         grad_ops.clip_finalize(None, None, self.total_sq, opt.max_grad_norm, coef_norm=opt._clip)
         return opt._clip[0:1]
 
@@ -264,6 +394,12 @@ class SymmZero1:
         """End of a step; the main stream is already ordered after the optimizer stream."""
         C, N = self.C, self.N
         if self.params:
+            # a tensor that received no gradient this step was not stepped (on any rank:
+            # the ranks run the same model); raise its flag so that nobody waits for it
+            for p in self.params:
+                if p not in self._signaled:
+                    C.signal(self._flag_ptrs(self.F_PARAM, self.index[p] * N + self.rank), self.epoch)
+            self._signaled.clear()
             C.wait_flags(self.flags, self.F_PARAM, len(self.params) * N, self.epoch, self.timeout_ms,
                          self.status, C.SYMM_TIMEOUT_PARAM)
         if self.small and self.small_reduced_epoch == self.epoch:
@@ -282,7 +418,7 @@ class SymmZero1:
             self.status_host.copy_(self.status)
         code = int(self.status_host[0])
         if code != 0:
-            names = {1: "a peer's gradient", 2: "a peer's parameter rows", 3: "the norm exchange"}
+            names = {1: "a peer's gradient", 2: "a peer's parameter rows", 3: "a scalar exchange"}
             raise RuntimeError(
                 f"DistributedOffloadAdam[rank {self.rank}]: device-side wait for "
                 f"{names.get(code, 'a peer')} timed out after {self.timeout_ms:.0f} ms; the step was "

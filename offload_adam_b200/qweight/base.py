@@ -142,6 +142,19 @@ class QWeightBase(Tensor):
     #: True when quantization needs max|x| over the whole tensor (a per-tensor scale)
     USES_TENSOR_AMAX = False
 
+    #: Format id of the fused optimizer kernels (``csrc/quant.h`` ``QFormat``), and the
+    #: names of the two payload tensors those kernels write: packed values, then scales.
+    KERNEL_FORMAT = 0
+    KERNEL_PAYLOAD: Tuple[str, str] = ("", "")
+
+    def kernel_group(self) -> int:
+        """Columns per scale of the fused kernels (NF4 block size, int4 group size)."""
+        return 0
+
+    def kernel_scale_dtype(self):
+        """Dtype of the stored scales when the format keeps them in the outer dtype."""
+        return torch.bfloat16
+
     def _payload_rows(self, lo: int, hi: int):
         """Per payload tensor, the view that holds output rows ``[lo, hi)`` of the
         weight (the whole tensor for per-tensor quantities)."""

@@ -125,6 +125,15 @@ class Int4QWeight(QWeightBase):
         out = (vals * self.scales.T.to(work).unsqueeze(-1)).reshape(self.shape)
         return out if dtype is None else out.to(dtype)
 
+    KERNEL_FORMAT = 3
+    KERNEL_PAYLOAD = ("qweight", "scales")
+
+    def kernel_group(self):
+        return self.group_size
+
+    def kernel_scale_dtype(self):
+        return self.scales.dtype
+
     def _payload_rows(self, lo, hi):
         # GPTQ stores (in, out): output rows are columns of both tensors
         return [self.qweight[:, lo:hi], self.scales[:, lo:hi]]

@@ -98,6 +98,12 @@ class Int8QWeight(QWeightBase):
         out = self.weight.to(work) * self.scales.to(work).unsqueeze(1)
         return out if dtype is None else out.to(dtype)
 
+    KERNEL_FORMAT = 4
+    KERNEL_PAYLOAD = ("weight", "scales")
+
+    def kernel_scale_dtype(self):
+        return self.scales.dtype
+
     def _payload_rows(self, lo, hi):
         return [self.weight[lo:hi], self.scales[lo:hi]]
 

@@ -143,6 +143,12 @@ class NF4QWeight(QWeightBase):
             return _dequant_nf4_cuda(self.weight_packed, self.absmax, self.in_f, self.blocksize, dtype)
         return dequantize_nf4_blockwise(self.weight_packed, self.absmax, self.in_f, self.blocksize, dtype)
 
+    KERNEL_FORMAT = 2
+    KERNEL_PAYLOAD = ("weight_packed", "absmax")
+
+    def kernel_group(self):
+        return self.blocksize
+
     def _payload_rows(self, lo, hi):
         per_row = self.in_f // self.blocksize
         return [self.weight_packed[lo:hi], self.absmax[lo * per_row:hi * per_row]]

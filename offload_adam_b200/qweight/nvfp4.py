@@ -179,6 +179,11 @@ class NVFP4QWeight(QWeightBase):
                                           self.in_f, dtype)
 
     USES_TENSOR_AMAX = True
+    KERNEL_FORMAT = 1
+    KERNEL_PAYLOAD = ("weight_packed", "block_scale_fp8")
+
+    def kernel_group(self):
+        return NVFP4_BLOCKSIZE
 
     def _payload_rows(self, lo, hi):
         return [self.weight_packed[lo:hi], self.block_scale_fp8[lo:hi], self.global_scale]

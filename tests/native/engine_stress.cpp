@@ -34,6 +34,23 @@ cudaError_t launch_adam_step(const AdamStepArgs& a, cudaStream_t s) {
   });
   return cudaSuccess;
 }
+// stand-in for the step of a quantized weight: the same update, plus one "packed" byte
+// per element (the low byte of the new m) stored at the element's place in the whole
+// weight, which checks the row arithmetic of chunked launches
+cudaError_t launch_adam_quant_push(const AdamStepArgs& a, const QuantPushArgs& q, cudaStream_t s) {
+  if (a.n % q.in_f != 0) return cudaErrorInvalidValue;
+  launch_adam_step(a, s);
+  AdamStepArgs c = a;
+  QuantPushArgs qq = q;
+  s->push([c, qq] {
+    const uint16_t* m = static_cast<const uint16_t*>(c.m);
+    for (int r = 0; r < qq.n_replicas; ++r) {
+      uint8_t* out = static_cast<uint8_t*>(qq.payload0[r]) + qq.row0 * qq.in_f;
+      for (int64_t i = 0; i < c.n; ++i) out[i] = (uint8_t)m[i];
+    }
+  });
+  return cudaSuccess;
+}
 // stand-in accumulate: out = a + b (uint16 arithmetic)
 cudaError_t launch_grad_accumulate(const AccumArgs& a, cudaStream_t s) {
   AccumArgs c = a;
@@ -56,7 +73,9 @@ struct Tensor {
   std::vector<float> x;
   std::vector<uint16_t> m0, v0;
   std::vector<float> x0;
+  std::vector<uint8_t> packed;  // "payload" of a quantized weight (stand-in)
 };
+constexpr int64_t kInF = 8;  // row length of the stand-in quantized weights
 
 static uint16_t seed_val(int pid, int64_t i, int salt) { return (uint16_t)((pid * 131 + i * 7 + salt * 1009) & 0x3fff); }
 
@@ -71,6 +90,9 @@ struct Scenario {
   bool destroy_busy = false;  // destroy the engine with transfers in flight: its destructor must finish them
   bool chaos = false;  // skipped tensors, repeated and cancelled plans, discards between steps
   int slow_h2d_us = 0, slow_d2h_us = 0;  // extra time per operation of the copy streams
+  int resident = 0;    // this many tensors (the last ones) keep their state in the staging buffer
+  bool quant = false;  // tensors are whole rows of kInF elements, stepped through the quantizing launch
+                       // in chunks of their own size
 };
 
 static int run(const Scenario& sc, unsigned seed) {
@@ -81,6 +103,8 @@ static int run(const Scenario& sc, unsigned seed) {
   for (int t = 0; t < sc.tensors; ++t) {
     Tensor& T = ts[t];
     T.n = 1 + rng() % (5 * sc.chunk);  // ragged: several chunks and a tail
+    if (sc.quant) T.n = (T.n + kInF - 1) / kInF * kInF;
+    T.packed.assign(T.n, 0);
     T.m.resize(T.n); T.v.resize(T.n); T.x.resize(T.n); T.p.assign(T.n, 0); T.g.resize(T.n); T.hg.assign(T.n, 0);
     for (int64_t i = 0; i < T.n; ++i) {
       T.m[i] = seed_val(t, i, 1); T.v[i] = seed_val(t, i, 2); T.x[i] = (float)seed_val(t, i, 3);
@@ -97,10 +121,18 @@ static int run(const Scenario& sc, unsigned seed) {
   opt.async_writeback = sc.async_writeback;
   size_t ring = OffloadEngine::min_ring_bytes(sc.chunk);
   if (sc.ring_fraction > 0) ring = std::max(ring, (size_t)(state_bytes * sc.ring_fraction) / 256 * 256);
+  size_t resident_need = 0;
+  for (int t = sc.tensors - sc.resident; t < sc.tensors; ++t)
+    resident_need += 2 * ((2 * ts[t].n + 255) / 256 * 256) + (4 * ts[t].n + 255) / 256 * 256;
+  ring += resident_need;
   void* ws = aligned_alloc(256, ring);
   int bad = 0;
+  // per-tensor chunk of the quantized stand-ins: whole rows, not the engine's default
+  const int64_t qchunk = sc.quant ? std::max<int64_t>(kInF, (sc.chunk - 3) / kInF * kInF) : 0;
   {
     OffloadEngine eng(0, &compute, &h2d, &d2h, ws, ring, opt, sc.tensors);
+    for (int t = sc.tensors - sc.resident; t < sc.tensors; ++t)
+      if (!eng.make_resident(t, oab::kModeFP32Master, ts[t].n)) { fprintf(stderr, "%s: make_resident refused\n", sc.name); ++bad; }
     std::vector<int> order(sc.tensors);
     for (int t = 0; t < sc.tensors; ++t) order[t] = t;
     for (int step = 0; step < sc.steps; ++step) {
@@ -111,6 +143,7 @@ static int run(const Scenario& sc, unsigned seed) {
           oab::StagedStepArgs a;
           a.pid = t; a.k.mode = oab::kModeFP32Master; a.k.n = ts[t].n;
           a.k.m = ts[t].m.data(); a.k.v = ts[t].v.data(); a.k.extra = ts[t].x.data();
+          a.chunk = qchunk;
           bool full = false;
           int64_t off = 0;
           while (off < ts[t].n && !full) {
@@ -138,6 +171,13 @@ static int run(const Scenario& sc, unsigned seed) {
         if (sc.host_grads) a.host_grad = T.hg.data();
         else a.k.g = T.g.data();
         a.k.m = T.m.data(); a.k.v = T.v.data(); a.k.extra = T.x.data();
+        oab::QuantPushArgs q;
+        if (sc.quant) {
+          q.format = oab::kQInt8; q.in_f = kInF; q.out_f = T.n / kInF; q.row0 = 0; q.n_replicas = 1;
+          q.payload0[0] = T.packed.data(); q.payload1[0] = T.packed.data();
+          a.quant = &q;
+          a.chunk = qchunk;
+        }
         eng.staged_step(a);
       }
       eng.join_compute(&compute);
@@ -150,6 +190,7 @@ static int run(const Scenario& sc, unsigned seed) {
           OffloadEngine::PrefetchItem it;
           it.pid = t; it.mode = oab::kModeFP32Master; it.n = ts[t].n;
           it.m = ts[t].m.data(); it.v = ts[t].v.data(); it.extra = ts[t].x.data();
+          it.chunk = qchunk;
           plan.push_back(it);
         }
         eng.start_prefetch(plan, 1 + rng() % 3);
@@ -178,7 +219,8 @@ static int run(const Scenario& sc, unsigned seed) {
       const uint16_t wm = (uint16_t)(T.m0[i] + T.stepped), wv = (uint16_t)(T.v0[i] + 2 * T.stepped);
       const float wx = T.x0[i] + (3.0f + (float)T.g[i]) * T.stepped;
       if (T.stepped == 0 && T.p[i] == 0) continue;  // never stepped: p was never written
-      if (T.m[i] != wm || T.v[i] != wv || T.x[i] != wx || T.p[i] != wm || T.hg[i] != (uint16_t)(2 * T.g[i])) {
+      const bool packed_ok = !sc.quant || T.packed[i] == (uint8_t)wm;
+      if (T.m[i] != wm || T.v[i] != wv || T.x[i] != wx || T.p[i] != wm || T.hg[i] != (uint16_t)(2 * T.g[i]) || !packed_ok) {
         // (the final gradient round trip leaves hg = g + g in every scenario)
         if (bad < 5)
           fprintf(stderr, "%s: tensor %d elem %lld: m %u/%u v %u/%u x %g/%g p %u hg %u/%u\n", sc.name, t,
@@ -211,6 +253,16 @@ int main(int argc, char** argv) {
       {"chaos",                         9, 10,  32, 0.6,  true,  true,  false, true,  12, false, false, true},
       {"slow write-backs",              8, 5,   64, 1.1,  true,  true,  false, false, 12, false, false, false, 0, 150},
       {"slow loads",                    8, 5,   64, 0.4,  true,  true,  false, false, 12, false, false, false, 150, 0},
+      //                                                                                      hostg  busy   chaos  slow    resident quant
+      {"all resident",                  6, 6,   64, 0.0,  true,  true,  false, false, 16, false, false, false, 0, 0,   6},
+      {"half resident, small ring",     9, 6,   32, 0.15, true,  true,  false, false, 8,  false, false, false, 0, 0,   4},
+      {"resident, inline, no plans",    6, 5,   64, 0.0,  false, false, false, false, 64, false, false, false, 0, 0,   3},
+      {"resident, chaos",               9, 10,  32, 0.5,  true,  true,  false, true,  12, false, false, true,  0, 0,   5},
+      {"resident, slow write-backs",    8, 5,   64, 0.3,  true,  true,  false, false, 12, false, false, false, 0, 150, 4},
+      {"resident, destroyed busy",      8, 4,   64, 0.3,  true,  true,  false, false, 16, false, true,  false, 0, 0,   4},
+      {"row chunks, quantizing launch", 8, 5,   64, 0.4,  true,  true,  false, false, 16, false, false, false, 0, 0,   0, true},
+      {"row chunks, resident",          8, 5,   64, 0.4,  true,  true,  false, true,  16, false, false, false, 0, 0,   3, true},
+      {"row chunks, caller loads",      7, 5,   64, 0.6,  true,  false, true,  false, 32, false, false, false, 0, 0,   0, true},
   };
   int bad = 0;
   for (int r = 0; r < rounds; ++r)

@@ -149,6 +149,10 @@ inline cudaError_t cudaMemcpyAsync(void* dst, const void* src, size_t n, cudaMem
   s->push([dst, src, n] { memcpy(dst, src, n); });
   return cudaSuccess;
 }
+inline cudaError_t cudaMemsetAsync(void* dst, int value, size_t n, cudaStream_t s) {
+  s->push([=] { memset(dst, value, n); });
+  return cudaSuccess;
+}
 inline cudaError_t cudaStreamSynchronize(cudaStream_t s) {
   s->drain();
   return cudaSuccess;

@@ -1,7 +1,7 @@
 """Debugging aids and host-state hand-offs of the offloaded optimizer: the serialized
 mode against the overlapped run, NVTX ranges, waiting for write-backs, and resuming
-into an optimizer that has already loaded state for its next step ahead of time; and the
-fake-quantization helper."""
+into an optimizer that has already loaded state for its next step ahead of time; state that
+stays resident in the staging buffer against state that streams through it."""
 
 import copy
 
@@ -107,22 +107,62 @@ def test_resume_into_an_optimizer_that_already_loaded_ahead(device):
     same(m_a, o_a, m_b, o_b)
 
 
-# ---------------------------------------------------------------- fake quantization
-@pytest.mark.parametrize("device", DEVICES)
-@pytest.mark.parametrize("fmt", ["nvfp4", "nf4", "int4", "int8"])
-def test_fake_quantize_is_quantize_then_dequantize_with_straight_through_gradient(fmt, device):
-    from offload_adam_b200.qweight import (Int4QWeight, Int8QWeight, NF4QWeight, NVFP4QWeight,
-                                           fake_quantize)
-    cls = {"nvfp4": NVFP4QWeight, "nf4": NF4QWeight, "int4": Int4QWeight, "int8": Int8QWeight}[fmt]
-    torch.manual_seed(2)
-    x = (torch.randn(64, 256, device=device) * 0.05).to(torch.bfloat16).requires_grad_(True)
-    y = fake_quantize(x, cls)
-    q = cls.from_float(torch.zeros(64, 256, dtype=torch.bfloat16, device=device))
-    q.copy_(x.detach().float() if device == "cuda" else x.detach())
-    assert y.dtype == x.dtype and torch.equal(y, q.dequantize(torch.bfloat16))
-    err = (y.float() - x.detach().float()).abs().max().item()
-    assert 0 < err < 0.05
-    (y.float() * 2).sum().backward()
-    assert torch.equal(x.grad, torch.full_like(x, 2.0))
-    with pytest.raises(ValueError):
-        fake_quantize(torch.randn(4, 7, device=device).to(torch.bfloat16), cls)
+# ------------------------------------------------- resident state vs streamed state
+@pytest.mark.gpu
+@pytest.mark.parametrize("clip", [None, 0.05])
+@pytest.mark.parametrize("staging", [1 << 20, 460 * 1024, 0])
+def test_resident_state_equals_streamed_state(clip, staging):
+    """Tensors whose state stays in the staging buffer (all of them, some of them, none)
+    must step to the same bits as tensors that are loaded every step, and the host copy
+    must be current after every step."""
+    device = "cuda"
+    batches = data(8, device)
+    m_a, m_b = net(device), net(device)
+    o_a = OffloadAdam(m_a, max_grad_norm=clip, keep_resident=False, **KW)
+    o_b = OffloadAdam(m_b, max_grad_norm=clip, staging_bytes=staging, **KW)
+    n_res = len(o_b._resident)
+    assert not o_a._resident
+    if staging == 1 << 20:
+        assert n_res == 4            # 4 x 128 x 128 x 8 B = 512 KiB of state fits
+    elif staging == 0:
+        assert n_res == 0
+    else:
+        assert n_res == 2            # the last two tensors stay, the first two stream
+    for s in range(4):
+        one_step(m_a, o_a, batches[2 * s:2 * s + 2])
+        one_step(m_b, o_b, batches[2 * s:2 * s + 2])
+        if s == 1:
+            o_b.wait_writeback()
+            o_a.wait_writeback()
+            torch.cuda.current_stream().synchronize()
+            same(m_a, o_a, m_b, o_b)
+    o_a.synchronize()
+    o_b.synchronize()
+    same(m_a, o_a, m_b, o_b)
+    h2d_a, _ = o_a._engine.bytes_moved()
+    h2d_b, _ = o_b._engine.bytes_moved()
+    if n_res == 4:
+        assert h2d_b * 3 < h2d_a  # loaded once instead of four times
+
+
+@pytest.mark.gpu
+def test_resume_reloads_resident_state():
+    device = "cuda"
+    batches = data(8, device)
+    m_a, m_b = net(device), net(device)
+    o_a = OffloadAdam(m_a, max_grad_norm=1.0, staging_bytes=1 << 20, **KW)
+    o_b = OffloadAdam(m_b, max_grad_norm=1.0, staging_bytes=1 << 20, **KW)
+    assert len(o_b._resident) == 4
+    one_step(m_a, o_a, batches[0:2])
+    one_step(m_a, o_a, batches[2:4])
+    one_step(m_b, o_b, batches[4:6])
+    sd = copy.deepcopy(o_a.state_dict())
+    o_b.load_offload_state_dict(sd)   # the resident copies of B are stale now
+    with torch.no_grad():
+        for p, q in zip(m_a.parameters(), m_b.parameters()):
+            q.copy_(p)
+    one_step(m_a, o_a, batches[6:8])
+    one_step(m_b, o_b, batches[6:8])
+    o_a.synchronize()
+    o_b.synchronize()
+    same(m_a, o_a, m_b, o_b)

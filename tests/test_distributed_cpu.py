@@ -415,17 +415,47 @@ def test_shard_gradient_layout_matches_its_restatement(residency, clip):
             assert torch.allclose(got[0][name].float(), want[name].float(), atol=2e-3, rtol=0), name
 
 
-def test_shard_gradient_layout_rejects_the_symmetric_path():
+def test_unknown_gradient_layout_is_rejected():
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(free_port())
     dist.init_process_group("gloo", rank=0, world_size=1)
     try:
         with pytest.raises(ValueError, match="grad_layout"):
-            DistributedOffloadAdam(make_net(), grad_layout="shard", comm="symm")
-        with pytest.raises(ValueError, match="grad_layout"):
             DistributedOffloadAdam(make_net(), grad_layout="rows")
     finally:
         dist.destroy_process_group()
+
+
+# ------------------------------------------- stochastic rounding: replicas must round alike
+def _sr_worker(rank, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        import random
+        random.seed(1000 + rank)  # the ranks' own generators differ, as in a real job
+        model = make_net()
+        # no seed given: rank 0's draw is broadcast
+        opt = DistributedOffloadAdam(model, lr=1e-2, weight_decay=0.05, mode="stochastic_rounding",
+                                     decoupled_weight_decay=True, inplace_param_threshold=200)
+        data = rank_batches(rank, 4)
+        for b in data:
+            opt.ready_for_optimizer_step = True
+            model(b).float().pow(2).mean().backward()
+            opt.step()
+        opt.synchronize()
+        torch.save({n: p.detach().clone() for n, p in model.named_parameters()},
+                   os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_stochastic_rounding_keeps_replicas_identical_without_a_seed():
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_sr_worker, args=(free_port(), d), nprocs=WORLD, join=True)
+        got = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(WORLD)]
+    for name in got[0]:
+        assert torch.equal(got[0][name], got[1][name]), f"replicas diverged: {name}"
 
 
 # ----------------------------------------------- checkpoints that move between world sizes

@@ -283,3 +283,46 @@ def test_row_shards_requantize_to_the_same_bits(fmt, device):
                 view.copy_(part)
     for a, b in zip(whole._payload(), split._payload()):
         assert _same_bits(a, b)
+
+
+# ---------------------------------------------------------------- fake quantization
+@pytest.mark.parametrize("device", ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)])
+@pytest.mark.parametrize("fmt", ["nvfp4", "nf4", "int4", "int8"])
+def test_fake_quantize_is_quantize_then_dequantize_with_straight_through_gradient(fmt, device):
+    from offload_adam_b200.qweight import fake_quantize
+    cls = {"nvfp4": NVFP4QWeight, "nf4": NF4QWeight, "int4": Int4QWeight, "int8": Int8QWeight}[fmt]
+    torch.manual_seed(2)
+    x = (torch.randn(64, 256, device=device) * 0.05).to(torch.bfloat16).requires_grad_(True)
+    y = fake_quantize(x, cls)
+    q = cls.from_float(torch.zeros(64, 256, dtype=torch.bfloat16, device=device))
+    q.copy_(x.detach().float() if device == "cuda" else x.detach())
+    assert y.dtype == x.dtype and torch.equal(y, q.dequantize(torch.bfloat16))
+    err = (y.float() - x.detach().float()).abs().max().item()
+    assert 0 < err < 0.05
+    (y.float() * 2).sum().backward()
+    assert torch.equal(x.grad, torch.full_like(x, 2.0))
+    with pytest.raises(ValueError):
+        fake_quantize(torch.randn(4, 7, device=device).to(torch.bfloat16), cls)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cls,kw", FORMATS, ids=IDS)
+@pytest.mark.parametrize("shape", [(96, 256), (33, 384), (5, 1024)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_gpu_one_pass_fake_quantize_equals_quantize_then_dequantize(cls, kw, shape, dtype):
+    """The one-pass kernel against the two kernels it replaces, bit for bit."""
+    from offload_adam_b200.qweight import fake_quantize
+    from offload_adam_b200.qweight.fake_quant import _fake_quantize_cuda
+    torch.manual_seed(shape[0] + shape[1])
+    x = (torch.randn(shape, device="cuda") * 0.07).to(dtype)
+    x[0, :16] = 0
+    x[1, 5] = 3.25
+    assert _fake_quantize_cuda(x, cls, kw) is not None  # the kernel route takes this case
+    y = fake_quantize(x, cls, **kw)
+    outer = torch.bfloat16 if dtype == torch.float32 else dtype
+    q = cls.from_float(torch.zeros(shape, dtype=outer, device="cuda"), **kw)
+    q.copy_(x)
+    want = q.dequantize(dtype)
+    assert y.dtype == dtype
+    bits = torch.int32 if dtype == torch.float32 else torch.int16
+    assert torch.equal(y.view(bits), want.view(bits))
