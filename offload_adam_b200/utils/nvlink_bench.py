@@ -165,7 +165,7 @@ def kernel_list(args):
     torch.manual_seed(0)
     model = nn.Sequential(nn.Linear(512, 2048, bias=False), nn.ReLU(), nn.Linear(2048, 512, bias=False),
                           nn.ReLU(), nn.Linear(512, 64, bias=True)).to(torch.bfloat16).cuda()
-    opt = DistributedOffloadAdam(model, lr=1e-3, mode="fp32_master", max_grad_norm=args.clip, comm="symm",
+    opt = DistributedOffloadAdam(model, lr=1e-3, mode="fp32_master", max_grad_norm=(args.clip if args.clip > 0 else None), comm="symm",
                                  decoupled_weight_decay=True, inplace_param_threshold=4096, chunk_elems=1 << 16)
     assert opt.comm == "symm"
     x = torch.randn(64, 512, device="cuda").to(torch.bfloat16)
@@ -215,7 +215,7 @@ def main():
     ap.add_argument("--link-gbs", type=float, default=770.0,
                     help="peer-copy rate per direction that fractions are quoted against")
     ap.add_argument("--kernel-list", action="store_true")
-    ap.add_argument("--clip", type=float, default=1.0)
+    ap.add_argument("--clip", type=float, default=1.0, help="--kernel-list: clipping threshold, 0 for the step-in-backward path")
     args = ap.parse_args()
     os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")

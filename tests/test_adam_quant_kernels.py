@@ -89,23 +89,23 @@ def test_fused_step_equals_step_then_quantize(fmt, group, shape, decoupled, pull
     assert torch.equal(master, want_master) and torch.equal(m, want_m) and torch.equal(v, want_v)
     # payload of the updated rows, from the format's PyTorch quantizer
     if fmt == "nf4":
-        packed, absmax = nf4.quantize_nf4_blockwise(want_master, group)
+        packed, absmax = nf4.quantize_nf4_blockwise(want_master.cpu(), group)
         per_row = in_f // group
         for a, b in pay:
-            assert torch.equal(a[row0:row0 + rows], packed)
-            assert torch.equal(b[row0 * per_row:(row0 + rows) * per_row], absmax)
+            assert torch.equal(a[row0:row0 + rows].cpu(), packed)
+            assert torch.equal(b[row0 * per_row:(row0 + rows) * per_row].cpu(), absmax)
             assert a[:row0].abs().sum() == 0 and a[row0 + rows:].abs().sum() == 0  # nothing outside the rows
     elif fmt == "int4":
-        qw, sc = int4.quantize_int4_groupwise(want_master, group, scale_dtype=scale_dtype)
+        qw, sc = int4.quantize_int4_groupwise(want_master.cpu(), group, scale_dtype=scale_dtype)
         for a, b in pay:
-            assert torch.equal(a[:, row0:row0 + rows], qw)
-            assert torch.equal(b[:, row0:row0 + rows], sc)
+            assert torch.equal(a[:, row0:row0 + rows].cpu(), qw)
+            assert torch.equal(b[:, row0:row0 + rows].cpu(), sc)
             assert a[:, :row0].abs().sum() == 0 and a[:, row0 + rows:].abs().sum() == 0
     else:
-        w, sc = int8.quantize_int8_per_channel(want_master, scale_dtype=scale_dtype)
+        w, sc = int8.quantize_int8_per_channel(want_master.cpu(), scale_dtype=scale_dtype)
         for a, b in pay:
-            assert torch.equal(a[row0:row0 + rows], w)
-            assert torch.equal(b[row0:row0 + rows], sc)
+            assert torch.equal(a[row0:row0 + rows].cpu(), w)
+            assert torch.equal(b[row0:row0 + rows].cpu(), sc)
             assert a[:row0].abs().sum() == 0 and a[row0 + rows:].abs().sum() == 0
 
 
@@ -134,11 +134,13 @@ def test_nvfp4_two_pass_step(shape):
                        [b.data_ptr() for _, b in pay], whole, gs)
     C.nvfp4_quantize_push(spec, copy.data_ptr(), copy.numel(), None, 0)
     torch.cuda.synchronize()
-    packed, scale, gscale = nvfp4.quantize_nvfp4_blockwise(want_master, amax=whole)
+    # the restatement runs on the CPU: a CUDA tensor divided by a Python scalar is multiplied by
+    # the scalar's reciprocal, which can differ from the correctly rounded quotient in the last bit
+    packed, scale, gscale = nvfp4.quantize_nvfp4_blockwise(want_master.cpu(), amax=whole.cpu())
     assert gs.item() == gscale.item()
     for a, b in pay:
-        assert torch.equal(a[row0:row0 + rows], packed)
-        assert torch.equal(b[row0:row0 + rows], scale.view(torch.uint8))
+        assert torch.equal(a[row0:row0 + rows].cpu(), packed)
+        assert torch.equal(b[row0:row0 + rows].cpu(), scale.view(torch.uint8))
         assert a[:row0].abs().sum() == 0 and a[row0 + rows:].abs().sum() == 0
 
 

@@ -166,7 +166,7 @@ def _bits(t):
     return t.view(torch.uint8) if t.element_size() == 1 else t
 
 
-def _qat_worker(rank, world, port, out_dir):
+def _qat_worker(rank, world, port, out_dir):  # noqa: C901
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     device = torch.device("cuda", rank)
@@ -178,28 +178,46 @@ def _qat_worker(rank, world, port, out_dir):
                                                quantize_linears)
         for name, cls in (("nvfp4", NVFP4QWeight), ("nf4", NF4QWeight), ("int4", Int4QWeight),
                           ("int8", Int8QWeight)):
-            torch.manual_seed(0)
-            model = QNet().to(torch.bfloat16).to(device)
-            quantize_linears(model, cls)
-            opt = DistributedOffloadAdam(model, lr=1e-2, weight_decay=0.01, mode="fp32_master",
-                                         max_grad_norm=1.0, decoupled_weight_decay=True, comm="nccl")
-            g = torch.Generator().manual_seed(7 + rank)
-            for _ in range(2):
-                opt.ready_for_optimizer_step = True
-                x = torch.randn(8, 256, generator=g).to(torch.bfloat16).to(device)
-                model(x).float().pow(2).mean().backward()
-                opt.step()
-            opt.synchronize()
-            ok = True
-            for p in model.parameters():
-                shard = opt.state[p]["master_params"].to(device)
-                full = torch.empty(p.shape, dtype=torch.float32, device=device)
-                dist.all_gather_into_tensor(full.view(-1), shard.view(-1))
-                want = cls.from_float(torch.zeros(p.shape, dtype=torch.bfloat16, device=device))
-                want.copy_(full)  # the gather-fp32-and-requantize-everything route
-                ok = ok and all(torch.equal(_bits(a), _bits(b))
-                                for a, b in zip(p.data._payload(), want._payload()))
-            report[name] = ok
+            for comm, clip in (("nccl", 1.0), ("symm", 1.0), ("symm", None)):
+                torch.manual_seed(0)
+                model = QNet().to(torch.bfloat16).to(device)
+                quantize_linears(model, cls)
+                # small chunks: every shard streams through the staging buffer in several pieces
+                opt = DistributedOffloadAdam(model, lr=1e-2, weight_decay=0.01, mode="fp32_master",
+                                             max_grad_norm=clip, decoupled_weight_decay=True, comm=comm,
+                                             chunk_elems=16384, wait_timeout_ms=20000,
+                                             keep_resident=(clip is None))
+                assert opt.comm == comm
+                if comm == "symm":
+                    assert all(opt._symm.handles(p) and opt._fused_quant_plan(p) is not None
+                               for p in model.parameters())
+                g = torch.Generator().manual_seed(7 + rank)
+                for _ in range(3):
+                    for micro in range(2):
+                        opt.ready_for_optimizer_step = micro == 1
+                        x = torch.randn(8, 256, generator=g).to(torch.bfloat16).to(device)
+                        (model(x).float().pow(2).mean() / 2).backward()
+                    opt.step()
+                opt.synchronize()
+                ok = True
+                for p in model.parameters():
+                    shard = opt.state[p]["master_params"].to(device)
+                    full = torch.empty(p.shape, dtype=torch.float32, device=device)
+                    dist.all_gather_into_tensor(full.view(-1), shard.view(-1))
+                    want = cls.from_float(torch.zeros(p.shape, dtype=torch.bfloat16, device=device))
+                    want.copy_(full)  # the gather-fp32-and-requantize-everything route
+                    ok = ok and all(torch.equal(_bits(a), _bits(b))
+                                    for a, b in zip(p.data._payload(), want._payload()))
+                    # every replica holds the same packed weight
+                    for t in p.data._payload():
+                        mine = _bits(t).contiguous()
+                        both = [torch.empty_like(mine) for _ in range(world)]
+                        dist.all_gather(both, mine)
+                        ok = ok and all(torch.equal(both[0], b) for b in both)
+                report[f"{name}/{comm}/{clip}"] = ok
+                del opt, model
+                torch.cuda.synchronize()
+                dist.barrier()
     finally:
         torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
         dist.destroy_process_group()
@@ -212,4 +230,168 @@ def test_sharded_qat_payload_matches_full_requantization():
         mp.spawn(_qat_worker, args=(2, free_port(), d), nprocs=2, join=True)
         reports = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(2)]
     for rep in reports:
-        assert rep == {"nvfp4": True, "nf4": True, "int4": True, "int8": True}, rep
+        assert len(rep) == 12 and all(rep.values()), rep
+
+
+# ------------------------------------ shard-sized gradient accumulators on the peer path
+def restatement_shard_layout(device, world, clip, ga, steps):
+    """grad_layout='shard' replayed on one GPU: every micro-batch's gradient is averaged
+    over the ranks first (fp32 sum in rank order, one rounding), then added to the
+    accumulator in bf16."""
+    from offload_adam_b200 import Adam
+    from offload_adam_b200.ops.adam_step import adam_step
+    mode = "fp32_master"
+    model = make_net(device)
+    ref = Adam(model.parameters(), lr=1e-2, weight_decay=0.05, mode=mode, decoupled_weight_decay=True)
+    data = [rank_batches(r, ga * steps, device) for r in range(world)]
+    scale = torch.tensor(1.0 / world, dtype=torch.float32, device=device)
+    params = list(model.parameters())
+    sharded = [p.dim() >= 1 and p.shape[0] % world == 0 and p.numel() >= 2000 for p in params]
+    for s in range(steps):
+        acc = [None] * len(params)
+        full = [[None] * len(params) for _ in range(world)]  # tensors that keep full-shape accumulators
+        for micro in range(ga):
+            per_rank = []
+            for r in range(world):
+                model.zero_grad()
+                (model(data[r][s * ga + micro]).float().pow(2).mean() / ga).backward()
+                per_rank.append([p.grad.detach().clone() for p in params])
+            for i in range(len(params)):
+                if sharded[i]:
+                    f = torch.zeros_like(per_rank[0][i], dtype=torch.float32)
+                    for r in range(world):
+                        f = f + per_rank[r][i].float()
+                    mean = (f * scale).to(torch.bfloat16)
+                    acc[i] = mean if acc[i] is None else (acc[i].float() + mean.float()).to(torch.bfloat16)
+                else:
+                    for r in range(world):
+                        g = per_rank[r][i]
+                        full[r][i] = g if full[r][i] is None else (full[r][i].float() + g.float()).to(torch.bfloat16)
+        for i in range(len(params)):
+            if not sharded[i]:
+                f = torch.zeros_like(full[0][i], dtype=torch.float32)
+                for r in range(world):
+                    f = f + full[r][i].float()
+                acc[i] = (f * scale).to(torch.bfloat16)
+        coef = None
+        if clip is not None:
+            total = torch.sqrt(sum((g.float() ** 2).sum() for g in acc))
+            coef = torch.clamp(clip / (total + 1e-6), max=1.0).reshape(1)
+        for p, g in zip(params, acc):
+            st = ref.state[p]
+            ref._init_state_if_empty(p, st)
+            st["step"] += 1
+            tensors = {k: st[k] for k in ref.config["states"]}
+            tensors["grad"] = g
+            adam_step(mode, p.data, tensors, 1e-2, 0.05, 0.9, 0.999, 1e-8, st["step"],
+                      decoupled_weight_decay=True, clip_coef=coef)
+    return [p.detach().clone() for p in params]
+
+
+def _shard_layout_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    report = {}
+    try:
+        from offload_adam_b200 import DistributedOffloadAdam
+        ga, steps = 3, 3
+        for clip in (None, 0.05):
+            model = make_net(device)
+            opt = DistributedOffloadAdam(model, lr=1e-2, weight_decay=0.05, mode="fp32_master", max_grad_norm=clip,
+                                         decoupled_weight_decay=True, inplace_param_threshold=2000, comm="symm",
+                                         grad_layout="shard", wait_timeout_ms=20000, chunk_elems=4096)
+            assert opt.comm == "symm" and opt._symm.shard_layout
+            data = rank_batches(rank, ga * steps, device)
+            k = 0
+            for _ in range(steps):
+                for micro in range(ga):
+                    opt.ready_for_optimizer_step = micro == ga - 1
+                    (model(data[k]).float().pow(2).mean() / ga).backward()
+                    k += 1
+                opt.step()
+            opt.synchronize()
+            got = [p.detach().clone() for p in model.parameters()]
+            want = restatement_shard_layout(device, world, clip, ga, steps)
+            same_everywhere = True
+            for p in got:
+                gathered = [torch.empty_like(p) for _ in range(world)]
+                dist.all_gather(gathered, p.contiguous())
+                same_everywhere = same_everywhere and all(torch.equal(gathered[0], g) for g in gathered)
+            report[str(clip)] = {
+                "replicas_equal": same_everywhere,
+                "exact": all(torch.equal(a, b) for a, b in zip(got, want)),
+                "near": all(torch.allclose(a.float(), b.float(), atol=4e-3, rtol=0) for a, b in zip(got, want)),
+            }
+            del opt, model
+            torch.cuda.synchronize()
+            dist.barrier()
+    finally:
+        torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
+        dist.destroy_process_group()
+
+
+def test_shard_gradient_layout_on_the_peer_path_matches_its_restatement():
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_shard_layout_worker, args=(world, free_port(), d), nprocs=world, join=True)
+        reports = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(world)]
+    for rep in reports:
+        assert set(rep) == {"None", "0.05"}, rep
+        for key, r in rep.items():
+            assert r["replicas_equal"] and r["near"], (key, r)
+            if key == "None":
+                assert r["exact"], (key, r)
+
+
+# --------------------------------- a parameter that gets no gradient must not stall the step
+class Branchy(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.used = nn.Linear(256, 256, bias=False)
+        self.unused = nn.Linear(256, 256, bias=False)
+
+    def forward(self, x):
+        return self.used(x)
+
+
+def _unused_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    report = {"ok": False}
+    try:
+        from offload_adam_b200 import DistributedOffloadAdam
+        for clip in (None, 1.0):
+            torch.manual_seed(0)
+            model = Branchy().to(torch.bfloat16).to(device)
+            before = model.unused.weight.detach().clone()
+            opt = DistributedOffloadAdam(model, lr=1e-2, mode="fp32_master", max_grad_norm=clip, comm="symm",
+                                         inplace_param_threshold=0, wait_timeout_ms=3000)
+            x = torch.randn(8, 256, device=device).to(torch.bfloat16)
+            for _ in range(2):
+                opt.ready_for_optimizer_step = True
+                model(x).float().pow(2).mean().backward()
+                opt.step()
+            opt.synchronize()  # raises if a bounded wait gave up
+            assert torch.equal(model.unused.weight, before)
+            assert opt.state[model.unused.weight]["step"] == 0 and opt.state[model.used.weight]["step"] == 2
+            del opt, model
+            dist.barrier()
+        report["ok"] = True
+    finally:
+        torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
+        dist.destroy_process_group()
+
+
+def test_parameter_without_gradient_does_not_stall_the_peer_path():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_unused_worker, args=(2, free_port(), d), nprocs=2, join=True)
+        reports = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(2)]
+    assert all(r["ok"] for r in reports), reports
