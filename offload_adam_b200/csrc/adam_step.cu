@@ -27,7 +27,7 @@ namespace {
 using namespace vec;
 
 template <int MODE, bool DECOUPLED, bool HAS_G2, bool PEERS, bool AMAX>
-__global__ void __launch_bounds__(kThreads, PEERS ? 2 : 3)
+__global__ void __launch_bounds__(kThreads, PEERS ? ((MODE == kModeSR || AMAX) ? 1 : 2) : 3)
 adam_step_kernel(Ptrs t, Peers pr, int64_t n, AdamScalars s, const float* __restrict__ clip_ptr,
                  uint64_t seed, int64_t elem_offset, float* amax_out, int vector_ok,
                  const int* abort_flag) {

@@ -91,17 +91,25 @@ __device__ __forceinline__ void load_vec(VecRegs<MODE>& r, const Ptrs& t, const 
   }
 }
 
-// One element.  p16/e16/master are in/out depending on MODE.
-template <int MODE, bool DECOUPLED>
-__device__ __forceinline__ float element_step(uint32_t& p16, uint32_t g16, bool has_g2,
-                                              uint32_t g2_16, uint32_t& m16, uint32_t& v16,
-                                              float& master, int16_t& err, float clip,
-                                              const AdamScalars& s, uint32_t rand16) {
+// One element: `p` is the full-precision parameter on entry and on exit, m and v the
+// moments (fp32 values of their bf16 storage on entry, unrounded on exit).
+template <bool DECOUPLED>
+__device__ __forceinline__ void element_math(float& p, uint32_t g16, bool has_g2, uint32_t g2_16,
+                                             float& m, float& v, float clip, const AdamScalars& s) {
   float g = bf16_bits_to_f32(g16);
   if (has_g2) {
     g = bf16_bits_to_f32(f32_to_bf16_rne_bits(__fadd_rn(g, bf16_bits_to_f32(g2_16))));
   }
   g = __fmul_rn(g, clip);
+  adam_math<DECOUPLED>(p, g, m, v, s);
+}
+
+// One element from and to its stored form (scalar tail path and multi-tensor kernel).
+template <int MODE, bool DECOUPLED>
+__device__ __forceinline__ float element_step(uint32_t& p16, uint32_t g16, bool has_g2,
+                                              uint32_t g2_16, uint32_t& m16, uint32_t& v16,
+                                              float& master, int16_t& err, float clip,
+                                              const AdamScalars& s, uint32_t rand16) {
   float m = bf16_bits_to_f32(m16);
   float v = bf16_bits_to_f32(v16);
   float p;
@@ -110,7 +118,7 @@ __device__ __forceinline__ float element_step(uint32_t& p16, uint32_t g16, bool 
   else if (MODE == kModeFP31) p = fp31_reconstruct(p16, err);
   else p = custom_reconstruct(p16, err);
 
-  adam_math<DECOUPLED>(p, g, m, v, s);
+  element_math<DECOUPLED>(p, g16, has_g2, g2_16, m, v, clip, s);
 
   m16 = f32_to_bf16_rne_bits(m);
   v16 = f32_to_bf16_rne_bits(v);
@@ -130,6 +138,8 @@ __device__ __forceinline__ float element_step(uint32_t& p16, uint32_t g16, bool 
 // Updates the 16 elements held in `r` in place: r.p receives the new bf16 parameter
 // (for fp32_master: bf16(master)), r.m / r.v the new moments, r.e0 / r.e1 the new
 // master (fp32_master) or rounding error.  Returns max |updated fp32 value| when AMAX.
+// Elements are handled in pairs, one 32-bit word of each bf16 stream at a time, so that
+// the roundings to bf16 are one hardware convert per pair and no half-word is masked in.
 template <int MODE, bool DECOUPLED, bool HAS_G2, bool AMAX>
 __device__ __forceinline__ float compute_vec(VecRegs<MODE>& r, int64_t vec, float clip,
                                              const AdamScalars& s, uint64_t seed, int64_t elem_offset) {
@@ -137,28 +147,45 @@ __device__ __forceinline__ float compute_vec(VecRegs<MODE>& r, int64_t vec, floa
   Philox4 rnd;
   float amax = 0.f;
 #pragma unroll
-  for (int j = 0; j < kVec; ++j) {
+  for (int w = 0; w < 8; ++w) {
     // one Philox block serves eight elements; it is drawn when its first element comes
     // up, so that only one block is alive at a time
-    if (MODE == kModeSR && (j & 7) == 0) rnd = philox4x32_10((uint64_t)((elem_offset + e) >> 3) + (j >> 3), seed);
-    uint32_t p16 = (MODE != kModeFP32Master) ? half_of(r.p, j) : 0u;
-    uint32_t m16 = half_of(r.m, j), v16 = half_of(r.v, j);
-    float master = 0.f;
-    int16_t err = 0;
-    if (MODE == kModeFP32Master) master = __uint_as_float(j < 8 ? r.e0.w[j & 7] : r.e1.w[j & 7]);
-    if (MODE == kModeFP31 || MODE == kModeCustom) err = (int16_t)half_of(r.e0, j);
-    uint32_t rand16 = (MODE == kModeSR) ? philox_word16(rnd, j & 7) : 0u;
-    float pf = element_step<MODE, DECOUPLED>(p16, half_of(r.g, j), HAS_G2,
-                                             HAS_G2 ? half_of(r.g2, j) : 0u, m16, v16, master,
-                                             err, clip, s, rand16);
-    if (AMAX) amax = fmaxf(amax, fabsf(pf));
-    set_half(r.p, j, p16);
-    set_half(r.m, j, m16);
-    set_half(r.v, j, v16);
-    if (MODE == kModeFP32Master) {
-      if (j < 8) r.e0.w[j & 7] = __float_as_uint(master); else r.e1.w[j & 7] = __float_as_uint(master);
+    if (MODE == kModeSR && (w & 3) == 0) rnd = philox4x32_10((uint64_t)((elem_offset + e) >> 3) + (w >> 2), seed);
+    const uint32_t gw = r.g.w[w], g2w = HAS_G2 ? r.g2.w[w] : 0u;
+    const uint32_t pw = (MODE != kModeFP32Master) ? r.p.w[w] : 0u;
+    float m[2] = {__uint_as_float(r.m.w[w] << 16), __uint_as_float(r.m.w[w] & 0xffff0000u)};
+    float v[2] = {__uint_as_float(r.v.w[w] << 16), __uint_as_float(r.v.w[w] & 0xffff0000u)};
+    float p[2];
+    uint32_t p16[2];
+    int16_t err[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int j = 2 * w + h;
+      const uint32_t pin = (pw >> (16 * h)) & 0xffffu;
+      if (MODE == kModeFP31 || MODE == kModeCustom) err[h] = (int16_t)half_of(r.e0, j);
+      if (MODE == kModeSR) p[h] = bf16_bits_to_f32(pin);
+      else if (MODE == kModeFP32Master) p[h] = __uint_as_float(j < 8 ? r.e0.w[j & 7] : r.e1.w[j & 7]);
+      else if (MODE == kModeFP31) p[h] = fp31_reconstruct(pin, err[h]);
+      else p[h] = custom_reconstruct(pin, err[h]);
+      element_math<DECOUPLED>(p[h], (gw >> (16 * h)) & 0xffffu, HAS_G2, (g2w >> (16 * h)) & 0xffffu,
+                              m[h], v[h], clip, s);
+      if (AMAX) amax = fmaxf(amax, fabsf(p[h]));
+      if (MODE == kModeSR) {
+        p16[h] = f32_to_bf16_sr_bits(p[h], philox_word16(rnd, j & 7));
+      } else if (MODE == kModeFP32Master) {
+        if (j < 8) r.e0.w[j & 7] = __float_as_uint(p[h]); else r.e1.w[j & 7] = __float_as_uint(p[h]);
+      } else if (MODE == kModeFP31) {
+        fp31_decompose(p[h], p16[h], err[h]);
+      } else {
+        custom_decompose(p[h], p16[h], err[h]);
+      }
     }
-    if (MODE == kModeFP31 || MODE == kModeCustom) set_half(r.e0, j, (uint32_t)(uint16_t)err);
+    r.m.w[w] = f32x2_to_bf16x2_rne(m[0], m[1]);
+    r.v.w[w] = f32x2_to_bf16x2_rne(v[0], v[1]);
+    if (MODE == kModeFP32Master) r.p.w[w] = f32x2_to_bf16x2_rne(p[0], p[1]);
+    else r.p.w[w] = (p16[0] & 0xffffu) | (p16[1] << 16);
+    if (MODE == kModeFP31 || MODE == kModeCustom)
+      r.e0.w[w] = (uint32_t)(uint16_t)err[0] | ((uint32_t)(uint16_t)err[1] << 16);
   }
   return amax;
 }

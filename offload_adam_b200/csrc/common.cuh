@@ -35,6 +35,15 @@ __device__ __forceinline__ uint32_t f32_to_bf16_rne_bits(float f) {
   return u >> 16;
 }
 
+// Two fp32 -> one word of two bf16 (lo in the low half), round to nearest even, with the
+// hardware convert.  Identical to f32_to_bf16_rne_bits for every non-NaN input; a NaN
+// comes out as 0x7fff instead of 0x7fc0 (still a NaN).
+__device__ __forceinline__ uint32_t f32x2_to_bf16x2_rne(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
 // 16 random bits decide whether the truncated bf16 moves one step away from
 // zero: up iff rand16 < low 16 bits of the fp32 pattern.
 __device__ __forceinline__ uint32_t f32_to_bf16_sr_bits(float f, uint32_t rand16) {

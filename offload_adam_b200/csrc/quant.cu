@@ -211,6 +211,53 @@ int8_quantize_kernel(const T* x, int64_t out_f, int64_t in_f, int8_t* q, S* scal
   }
 }
 
+// Same result, for rows of at most kThreads * VPT * 16 columns that start 32-byte aligned:
+// every thread keeps its VPT vectors of the row in registers between the maximum and the
+// rounding, so the row is read once.
+template <typename T, typename S, bool FAKE, int VPT>
+__global__ void __launch_bounds__(kThreads)
+int8_quantize_cached_kernel(const T* x, int64_t out_f, int64_t in_f, int8_t* q, S* scales, T* out) {
+  __shared__ float red[kThreads / 32];
+  __shared__ float s_inv, s_scale;
+  const int nvec = (int)(in_f >> 4);
+  for (int64_t row = blockIdx.x; row < out_f; row += gridDim.x) {
+    const T* xr = x + row * in_f;
+    float e[VPT][16];
+    float m = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int v = threadIdx.x + k * kThreads;
+      if (v < nvec) {
+        Elem<T>::load16(xr + (int64_t)v * 16, e[k]);
+        m = fmaxf(m, amax16(e[k]));
+      }
+    }
+    const float bm = block_max<kThreads>(m, red);
+    if (threadIdx.x == 0) {
+      const float scale = __fdiv_rn(bm, 127.0f);
+      if (!FAKE) scales[row] = Elem<S>::from_f32(scale);
+      s_scale = stored_scale<S>(scale);
+      s_inv = rcp_rn(fmaxf(scale, kEps));
+    }
+    __syncthreads();
+    const float inv = s_inv, sc = s_scale;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int v = threadIdx.x + k * kThreads;
+      if (v < nvec) {
+        if (FAKE) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) e[k][i] = round_like_dequant<T, S>(__fmul_rn((float)int8_round(e[k][i], inv), sc));
+          Elem<T>::store16(out + row * in_f + (int64_t)v * 16, e[k]);
+        } else {
+          *reinterpret_cast<uint4*>(q + row * in_f + (int64_t)v * 16) = int8_pack16(e[k], inv);
+        }
+      }
+    }
+    __syncthreads();  // s_inv / s_scale are rewritten for the next row
+  }
+}
+
 // out = S(q) * scale, computed and rounded in S
 template <typename S>
 __global__ void __launch_bounds__(kThreads)
@@ -221,7 +268,9 @@ int8_dequantize_kernel(const int8_t* q, const S* scales, int64_t out_f, int64_t 
   if (vec) {
     const int64_t nvec = n >> 4;
     for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * kThreads) {
-      const float s = Elem<S>::to_f32(scales[(v * 16) / in_f]);
+      // 32-bit division when the row index fits (it always does for weights)
+      const int64_t row = (n < (int64_t(1) << 31)) ? (int64_t)((uint32_t)(v * 16) / (uint32_t)in_f) : (v * 16) / in_f;
+      const float s = Elem<S>::to_f32(scales[row]);
       const uint4 w4 = *reinterpret_cast<const uint4*>(q + v * 16);
       const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
       float e[16];
@@ -239,39 +288,59 @@ int8_dequantize_kernel(const int8_t* q, const S* scales, int64_t out_f, int64_t 
 // Tile = 32 rows x 128 columns (see Int4Tile): every thread moves 16 consecutive
 // elements of a row with one (bf16/fp16) or two (fp32) 256-bit accesses; the packed
 // words are transposed through shared memory.
+// A CTA works on kInt4Tiles neighbouring tiles of one 32-row band: all of their loads
+// are issued before the first use, which keeps enough bytes in flight per SM.
+constexpr int kInt4Tiles = 4;
+
 template <typename T, typename S>
 __global__ void __launch_bounds__(kThreads)
 int4_quantize_kernel(const T* x, int64_t out_f, int64_t in_f, int group, int32_t* qweight, S* scales, int aligned) {
-  __shared__ Int4Tile sm;
+  __shared__ Int4Tile sm[kInt4Tiles];
   const int64_t row0 = (int64_t)blockIdx.x * 32;
-  const int64_t col0 = (int64_t)blockIdx.y * 128;
+  const int64_t tile0 = (int64_t)blockIdx.y * kInt4Tiles, ntiles = in_f >> 7;
   const int lr = threadIdx.x >> 3, seg = threadIdx.x & 7;
-  float e[16];
-  if (row0 + lr < out_f) load16_any(x + (row0 + lr) * in_f + col0 + seg * 16, e, aligned != 0);
-  else {
+  const bool row_ok = row0 + lr < out_f;
+  float e[kInt4Tiles][16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) e[i] = 0.f;
+  for (int t = 0; t < kInt4Tiles; ++t) {
+    if (row_ok && tile0 + t < ntiles) load16_any(x + (row0 + lr) * in_f + ((tile0 + t) << 7) + seg * 16, e[t], aligned != 0);
+    else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) e[t][i] = 0.f;
+    }
   }
-  int4_tile_quantize(e, group, sm);
+#pragma unroll
+  for (int t = 0; t < kInt4Tiles; ++t) int4_tile_quantize(e[t], group, sm[t]);
   __syncthreads();
   const int64_t left = out_f - row0;
-  int4_tile_store<S>(sm, out_f, row0, left < 32 ? (int)left : 32, col0, group, qweight, scales);
+  const int valid = left < 32 ? (int)left : 32;
+#pragma unroll
+  for (int t = 0; t < kInt4Tiles; ++t)
+    if (tile0 + t < ntiles) int4_tile_store<S>(sm[t], out_f, row0, valid, (tile0 + t) << 7, group, qweight, scales);
 }
 
 template <typename S>
 __global__ void __launch_bounds__(kThreads)
 int4_dequantize_kernel(const int32_t* qweight, const S* scales, int64_t out_f, int64_t in_f, int group, S* out, int aligned) {
-  __shared__ Int4Tile sm;
+  __shared__ Int4Tile sm[kInt4Tiles];
   const int64_t row0 = (int64_t)blockIdx.x * 32;
-  const int64_t col0 = (int64_t)blockIdx.y * 128;
+  const int64_t tile0 = (int64_t)blockIdx.y * kInt4Tiles, ntiles = in_f >> 7;
   const int64_t left = out_f - row0;
-  int4_tile_load<S>(sm, out_f, row0, left < 32 ? (int)left : 32, col0, group, qweight, scales);
+  const int valid = left < 32 ? (int)left : 32;
+#pragma unroll
+  for (int t = 0; t < kInt4Tiles; ++t)
+    if (tile0 + t < ntiles) int4_tile_load<S>(sm[t], out_f, row0, valid, (tile0 + t) << 7, group, qweight, scales);
   __syncthreads();
   const int lr = threadIdx.x >> 3, seg = threadIdx.x & 7;
   if (row0 + lr >= out_f) return;
-  float e[16];
-  int4_unpack16((uint32_t)sm.words[seg * 2][lr], (uint32_t)sm.words[seg * 2 + 1][lr], sm.scale[(seg * 16) / group][lr], e);
-  store16_any(out + (row0 + lr) * in_f + col0 + seg * 16, e, aligned != 0);
+#pragma unroll
+  for (int t = 0; t < kInt4Tiles; ++t) {
+    if (tile0 + t >= ntiles) break;
+    float e[16];
+    int4_unpack16((uint32_t)sm[t].words[seg * 2][lr], (uint32_t)sm[t].words[seg * 2 + 1][lr],
+                  sm[t].scale[(seg * 16) / group][lr], e);
+    store16_any(out + (row0 + lr) * in_f + ((tile0 + t) << 7) + seg * 16, e, aligned != 0);
+  }
 }
 
 // dq(q(x)) for int4 needs no transposition: one thread per 16 elements of a row, a
@@ -373,13 +442,25 @@ cudaError_t launch_nf4_dequantize(const uint8_t* packed, const float* absmax, in
   return cudaGetLastError();
 }
 
+// rows that fit the register-cached kernel (aligned, whole vectors) take it
+#define OAB_INT8_LAUNCH(FAKE, Q, SC, OUT)                                                              \
+  do {                                                                                                 \
+    const bool fits = in_f % 16 == 0 && aligned32(x) && (FAKE ? aligned32(OUT) : ((reinterpret_cast<uintptr_t>(Q) & 15u) == 0)); \
+    if (fits && in_f <= kThreads * 16)                                                                 \
+      int8_quantize_cached_kernel<T, S, FAKE, 1><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, Q, SC, OUT); \
+    else if (fits && in_f <= kThreads * 16 * 4)                                                        \
+      int8_quantize_cached_kernel<T, S, FAKE, 4><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, Q, SC, OUT); \
+    else                                                                                               \
+      int8_quantize_kernel<T, S, FAKE><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, Q, SC, OUT); \
+  } while (0)
+
 cudaError_t launch_int8_quantize(const void* x, int dtype, int64_t out_f, int64_t in_f, int8_t* q,
                                  void* scales, int scale_dtype, cudaStream_t st) {
   if (out_f <= 0) return cudaSuccess;
   const unsigned grid = (unsigned)(out_f < (int64_t)kNumSMs * 16 ? out_f : (int64_t)kNumSMs * 16);
   count_launch();
   OAB_DISPATCH_IN(dtype, OAB_DISPATCH_SCALE(scale_dtype,
-      int8_quantize_kernel<T, S, false><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, q, (S*)scales, nullptr)));
+      OAB_INT8_LAUNCH(false, q, (S*)scales, nullptr)));
   return cudaGetLastError();
 }
 
@@ -395,7 +476,7 @@ cudaError_t launch_int4_quantize(const void* x, int dtype, int64_t out_f, int64_
                                  int32_t* qweight, void* scales, int scale_dtype, cudaStream_t st) {
   if (out_f <= 0) return cudaSuccess;
   if (in_f % 128 != 0 || (group != 32 && group != 64 && group != 128)) return cudaErrorInvalidValue;
-  dim3 grid((unsigned)((out_f + 31) / 32), (unsigned)(in_f / 128));
+  dim3 grid((unsigned)((out_f + 31) / 32), (unsigned)((in_f / 128 + kInt4Tiles - 1) / kInt4Tiles));
   count_launch();
   OAB_DISPATCH_IN(dtype, OAB_DISPATCH_SCALE(scale_dtype,
       int4_quantize_kernel<T, S><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, group, qweight, (S*)scales, aligned32(x) ? 1 : 0)));
@@ -406,7 +487,7 @@ cudaError_t launch_int4_dequantize(const int32_t* qweight, const void* scales, i
                                    int64_t in_f, int group, void* out, cudaStream_t st) {
   if (out_f <= 0) return cudaSuccess;
   if (in_f % 128 != 0 || (group != 32 && group != 64 && group != 128)) return cudaErrorInvalidValue;
-  dim3 grid((unsigned)((out_f + 31) / 32), (unsigned)(in_f / 128));
+  dim3 grid((unsigned)((out_f + 31) / 32), (unsigned)((in_f / 128 + kInt4Tiles - 1) / kInt4Tiles));
   count_launch();
   OAB_DISPATCH_SCALE(scale_dtype, int4_dequantize_kernel<S><<<grid, kThreads, 0, st>>>(qweight, (const S*)scales, out_f, in_f, group, (S*)out, aligned32(out) ? 1 : 0));
   return cudaGetLastError();
@@ -445,7 +526,7 @@ cudaError_t launch_fake_quant(int format, const void* x, void* out, int dtype, i
     case kQInt8: {
       const unsigned grid = (unsigned)(out_f < (int64_t)kNumSMs * 16 ? out_f : (int64_t)kNumSMs * 16);
       OAB_DISPATCH_IN(dtype, OAB_DISPATCH_SCALE(scale_dtype,
-          int8_quantize_kernel<T, S, true><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, nullptr, nullptr, (T*)out)));
+          OAB_INT8_LAUNCH(true, nullptr, (S*)nullptr, (T*)out)));
       break;
     }
     default: return cudaErrorInvalidValue;

@@ -114,27 +114,30 @@ static __constant__ float kNF4[16] = {
     0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
     0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
 
-// index of the nearest codebook entry; among equal distances the lowest index wins
-// (the rule of a sequential scan with a strict '<').  A 4-step bisection on the
-// midpoints finds a candidate, its two neighbours settle rounding and ties.
-__device__ __forceinline__ int nf4_nearest(float x, const float* lut) {
-  int lo = 0;
-#pragma unroll
-  for (int step = 8; step > 0; step >>= 1) {
-    int mid = lo + step;  // compare against the midpoint between mid-1 and mid
-    float mp = 0.5f * (lut[mid - 1] + lut[mid]);
-    lo = (x > mp) ? mid : lo;
-  }
-  int best = lo > 0 ? lo - 1 : lo;
-  float bd = fabsf(__fsub_rn(x, lut[best]));
-  int hi = lo < 15 ? lo + 1 : lo;
-  for (int c = best + 1; c <= hi; ++c) {
-    float d = fabsf(__fsub_rn(x, lut[c]));
-    if (d < bd) { bd = d; best = c; }
-  }
-  return best;
+// Index of the nearest codebook entry; among equal distances the lowest index wins (the
+// rule of a sequential scan over the 16 entries with a strict '<' on
+// |fl(x - entry)|).  For neighbouring entries i, i + 1 the outcome "i + 1 is strictly
+// closer" is monotone in x, so it is decided by one threshold: kNF4Threshold[i] is the
+// smallest fp32 x for which |fl(x - entry[i+1])| < |fl(x - entry[i])|, found by bisection
+// over the fp32 values between the two entries (tests/test_qweight_formats.py recomputes
+// the table from the codebook).  The index is the number of thresholds <= x: a four-step
+// binary search over constants, no table look-ups.
+#define OAB_NF4_THRESHOLD_BITS                                                                      \
+  0xbf591cd8u, 0xbf1c5270u, 0xbeeb847fu, 0xbeadea76u, 0xbe703cecu, 0xbe0d38bbu, 0xbd3a7870u,        \
+  0x3d22fb00u, 0x3df64863u, 0x3e5067e1u, 0x3e9582d5u, 0x3ec753fau, 0x3f006d04u, 0x3f248db0u, 0x3f5c89dau
+__device__ __forceinline__ int nf4_nearest(float x, const float* /*lut*/) {
+  constexpr uint32_t B[15] = {OAB_NF4_THRESHOLD_BITS};
+#define OAB_T(i) __uint_as_float(B[i])
+  const bool c3 = x >= OAB_T(7);
+  const bool c2 = x >= (c3 ? OAB_T(11) : OAB_T(3));
+  const float t1 = c3 ? (c2 ? OAB_T(13) : OAB_T(9)) : (c2 ? OAB_T(5) : OAB_T(1));
+  const bool c1 = x >= t1;
+  const float t0 = c3 ? (c2 ? (c1 ? OAB_T(14) : OAB_T(12)) : (c1 ? OAB_T(10) : OAB_T(8)))
+                      : (c2 ? (c1 ? OAB_T(6) : OAB_T(4)) : (c1 ? OAB_T(2) : OAB_T(0)));
+  const bool c0 = x >= t0;
+#undef OAB_T
+  return (c3 ? 8 : 0) | (c2 ? 4 : 0) | (c1 ? 2 : 0) | (c0 ? 1 : 0);
 }
-
 
 // ---------------------------------------------------------------- 16-value packers
 // NVFP4: e4m3 block scale + two words of E2M1 codes (even element in the low nibble).

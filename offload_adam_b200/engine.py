@@ -76,14 +76,14 @@ class TransferEngine:
                     # circular staging buffer: pipelines the chunks of a step and doubles as
                     # the early-H2D / trailing-D2H area
                     chunk_elems = max(16, int(chunk_elems) // 16 * 16)
+                    # smallest ring that pipelines a step: the engine's floor plus `ring_slots`
+                    # full-width chunks.  `staging_bytes` comes on top of it: that part buys
+                    # overlap (early loads, trailing write-backs) or residency.
                     floor = self.C.OffloadEngine.min_ring_bytes(chunk_elems)
-                    # the floor on top of the request: with all of a small shard's state
-                    # prefetched, the chunks loaded during the step still find room
-                    nbytes = max(int(ring_slots) * chunk_elems * 10, int(staging_bytes)) + floor
                     self.chunk_elems = chunk_elems
                     self._ring_floor_extra = int(ring_slots) * chunk_elems * 10
-                    nbytes = (nbytes + 255) // 256 * 256
-                    smallest = (max(int(ring_slots) * chunk_elems * 10, floor) + 255) // 256 * 256
+                    smallest = (floor + self._ring_floor_extra + 255) // 256 * 256
+                    nbytes = (smallest + max(0, int(staging_bytes)) + 255) // 256 * 256
                     while True:
                         # the buffer only buys overlap: when memory is short, take less
                         try:

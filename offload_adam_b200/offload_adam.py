@@ -493,7 +493,9 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
 
     # ------------------------------------------------------------ hook bodies
     def _resolve_staging_bytes(self, staging_bytes):
-        state = self._estimate_pinned_bytes(self._offload_params)
+        # the state itself plus the padding of its tensors: with that much everything can
+        # stay resident, and more buys nothing
+        state = self._estimate_pinned_bytes(self._offload_params) + 768 * len(self._offload_params)
         if staging_bytes is None:
             staging_bytes = state
             if self._cuda:

@@ -110,7 +110,7 @@ def test_resume_into_an_optimizer_that_already_loaded_ahead(device):
 # ------------------------------------------------- resident state vs streamed state
 @pytest.mark.gpu
 @pytest.mark.parametrize("clip", [None, 0.05])
-@pytest.mark.parametrize("staging", [1 << 20, 460 * 1024, 0])
+@pytest.mark.parametrize("staging", [1 << 20, 300 * 1024, 0])
 def test_resident_state_equals_streamed_state(clip, staging):
     """Tensors whose state stays in the staging buffer (all of them, some of them, none)
     must step to the same bits as tensors that are loaded every step, and the host copy

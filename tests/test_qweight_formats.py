@@ -326,3 +326,59 @@ def test_gpu_one_pass_fake_quantize_equals_quantize_then_dequantize(cls, kw, sha
     assert y.dtype == dtype
     bits = torch.int32 if dtype == torch.float32 else torch.int16
     assert torch.equal(y.view(bits), want.view(bits))
+
+
+# ------------------------------------------ NF4 decision thresholds built into the kernels
+def test_nf4_kernel_thresholds_follow_from_the_codebook():
+    """The CUDA kernels find the nearest NF4 entry by counting thresholds <= x.  Threshold i is
+    the smallest fp32 x for which entry i + 1 is strictly closer than entry i in fp32
+    arithmetic; recompute all fifteen by bisection over fp32 values and compare with the
+    table in csrc/quant_math.cuh, then check the counting rule against the sequential scan."""
+    import os
+    import re
+
+    import numpy as np
+    lut = np.array(nf4.NF4_LUT, dtype=np.float32)
+
+    def to_ord(x):
+        u = int(np.float32(x).view(np.uint32))
+        return u + 0x80000000 if u < 0x80000000 else 0xFFFFFFFF - u
+
+    def from_ord(o):
+        u = o - 0x80000000 if o >= 0x80000000 else 0xFFFFFFFF - o
+        return np.uint32(u).view(np.float32)
+
+    def closer_to_next(x, i):
+        x = np.float32(x)
+        return abs(np.float32(x - lut[i + 1])) < abs(np.float32(x - lut[i]))
+
+    want = []
+    for i in range(15):
+        lo, hi = to_ord(lut[i]), to_ord(lut[i + 1])
+        while hi - lo > 1:
+            mid = (lo + hi) // 2
+            if closer_to_next(from_ord(mid), i):
+                hi = mid
+            else:
+                lo = mid
+        want.append(int(from_ord(hi).view(np.uint32)))
+    header = os.path.join(os.path.dirname(nf4.__file__), "..", "csrc", "quant_math.cuh")
+    text = open(header).read()
+    block = text[text.index("#define OAB_NF4_THRESHOLD_BITS"):]
+    block = block[:block.index("__device__")]
+    got = [int(h, 16) for h in re.findall(r"0x([0-9a-fA-F]{8})u", block)]
+    assert got == want
+    # the counting rule equals the restatement's sequential scan, also next to every threshold
+    thr = np.array(want, dtype=np.uint32).view(np.float32)
+    rng = np.random.default_rng(0)
+    xs = np.concatenate([rng.uniform(-1.05, 1.05, 200000).astype(np.float32), thr,
+                         np.nextafter(thr, np.float32(-2)), np.nextafter(thr, np.float32(2))])
+    count = sum((xs >= t).astype(np.int64) for t in thr)
+    best = np.zeros(xs.shape, dtype=np.int64)
+    bd = np.full(xs.shape, np.inf, dtype=np.float32)
+    for i, v in enumerate(lut):
+        d = np.abs((xs - v).astype(np.float32))
+        c = d < bd
+        best[c] = i
+        bd[c] = d[c]
+    assert np.array_equal(count, best)
