@@ -288,11 +288,12 @@ int8_dequantize_kernel(const int8_t* q, const S* scales, int64_t out_f, int64_t 
 // Tile = 32 rows x 128 columns (see Int4Tile): every thread moves 16 consecutive
 // elements of a row with one (bf16/fp16) or two (fp32) 256-bit accesses; the packed
 // words are transposed through shared memory.
-// A CTA works on kInt4Tiles neighbouring tiles of one 32-row band: all of their loads
-// are issued before the first use, which keeps enough bytes in flight per SM.
-constexpr int kInt4Tiles = 4;
+// A CTA works on TILES neighbouring tiles of one 32-row band, all of their loads issued
+// before the first use.  Measured on B200: de-quantization (few registers, latency of
+// the transposed loads exposed) gains from four tiles, quantization is fastest with one.
+constexpr int kInt4QuantTiles = 1, kInt4DequantTiles = 4;
 
-template <typename T, typename S>
+template <typename T, typename S, int kInt4Tiles>
 __global__ void __launch_bounds__(kThreads)
 int4_quantize_kernel(const T* x, int64_t out_f, int64_t in_f, int group, int32_t* qweight, S* scales, int aligned) {
   __shared__ Int4Tile sm[kInt4Tiles];
@@ -319,7 +320,7 @@ int4_quantize_kernel(const T* x, int64_t out_f, int64_t in_f, int group, int32_t
     if (tile0 + t < ntiles) int4_tile_store<S>(sm[t], out_f, row0, valid, (tile0 + t) << 7, group, qweight, scales);
 }
 
-template <typename S>
+template <typename S, int kInt4Tiles>
 __global__ void __launch_bounds__(kThreads)
 int4_dequantize_kernel(const int32_t* qweight, const S* scales, int64_t out_f, int64_t in_f, int group, S* out, int aligned) {
   __shared__ Int4Tile sm[kInt4Tiles];
@@ -476,10 +477,10 @@ cudaError_t launch_int4_quantize(const void* x, int dtype, int64_t out_f, int64_
                                  int32_t* qweight, void* scales, int scale_dtype, cudaStream_t st) {
   if (out_f <= 0) return cudaSuccess;
   if (in_f % 128 != 0 || (group != 32 && group != 64 && group != 128)) return cudaErrorInvalidValue;
-  dim3 grid((unsigned)((out_f + 31) / 32), (unsigned)((in_f / 128 + kInt4Tiles - 1) / kInt4Tiles));
+  dim3 grid((unsigned)((out_f + 31) / 32), (unsigned)((in_f / 128 + kInt4QuantTiles - 1) / kInt4QuantTiles));
   count_launch();
   OAB_DISPATCH_IN(dtype, OAB_DISPATCH_SCALE(scale_dtype,
-      int4_quantize_kernel<T, S><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, group, qweight, (S*)scales, aligned32(x) ? 1 : 0)));
+      int4_quantize_kernel<T, S, kInt4QuantTiles><<<grid, kThreads, 0, st>>>((const T*)x, out_f, in_f, group, qweight, (S*)scales, aligned32(x) ? 1 : 0)));
   return cudaGetLastError();
 }
 
@@ -487,9 +488,9 @@ cudaError_t launch_int4_dequantize(const int32_t* qweight, const void* scales, i
                                    int64_t in_f, int group, void* out, cudaStream_t st) {
   if (out_f <= 0) return cudaSuccess;
   if (in_f % 128 != 0 || (group != 32 && group != 64 && group != 128)) return cudaErrorInvalidValue;
-  dim3 grid((unsigned)((out_f + 31) / 32), (unsigned)((in_f / 128 + kInt4Tiles - 1) / kInt4Tiles));
+  dim3 grid((unsigned)((out_f + 31) / 32), (unsigned)((in_f / 128 + kInt4DequantTiles - 1) / kInt4DequantTiles));
   count_launch();
-  OAB_DISPATCH_SCALE(scale_dtype, int4_dequantize_kernel<S><<<grid, kThreads, 0, st>>>(qweight, (const S*)scales, out_f, in_f, group, (S*)out, aligned32(out) ? 1 : 0));
+  OAB_DISPATCH_SCALE(scale_dtype, int4_dequantize_kernel<S, kInt4DequantTiles><<<grid, kThreads, 0, st>>>(qweight, (const S*)scales, out_f, in_f, group, (S*)out, aligned32(out) ? 1 : 0));
   return cudaGetLastError();
 }
 

@@ -44,7 +44,7 @@ template <> struct Elem<__nv_bfloat16> {
   static __device__ __forceinline__ void store16(__nv_bfloat16* p, const float (&x)[16]) {
     V8 a;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) a.w[i] = f32_to_bf16_rne_bits(x[2 * i]) | (f32_to_bf16_rne_bits(x[2 * i + 1]) << 16);
+    for (int i = 0; i < 8; ++i) a.w[i] = f32x2_to_bf16x2_rne(x[2 * i], x[2 * i + 1]);
     st32_stream(p, a);
   }
   static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -178,7 +178,6 @@ def test_offloaded_qat_steps_like_the_on_gpu_optimizer(name, cls, kw, resident):
     ob = OffloadAdam(mb, mode="fp32_master", lr=1e-2, weight_decay=0.05, decoupled_weight_decay=True,
                      inplace_param_threshold=0, chunk_elems=4096, keep_resident=resident,
                      staging_bytes=(4 << 20) if resident else 0, max_grad_norm=None)
-    assert not resident or ob._engine.staging_bytes > 3 << 20
     assert all(ob._fused_quant_plan(p) is not None for p in mb.parameters())
     assert (len(ob._resident) == 3) == resident
     g = torch.Generator().manual_seed(3)
