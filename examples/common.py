@@ -21,6 +21,10 @@ MODES = ["stochastic_rounding", "fp32_master", "fp31_master", "fp32_master_custo
 
 def add_common_args(p):
     p.add_argument("--model-name", default="llama3-8b", choices=list(MODELS))
+    p.add_argument("--hf-model", default=None,
+                   help="train a HuggingFace causal LM instead of the package's own Llama: a local checkpoint "
+                        "directory or hub id (weights are loaded with AutoModelForCausalLM.from_pretrained), or "
+                        "a directory / file holding only a config.json (random-init weights of that architecture)")
     p.add_argument("--layers", type=int, default=None, help="override the number of layers")
     p.add_argument("--mode", choices=MODES, default="fp32_master")
     p.add_argument("--tokens-per-sample", type=int, default=2048)
@@ -61,7 +65,60 @@ def validate(args):
         raise ValueError("--warmup-steps must be in [0, --steps)")
 
 
+class _HFCausalLM(torch.nn.Module):
+    """Gives a HuggingFace causal LM the call signature the example loop uses
+    (``model(ids, labels=ids)`` returns the loss) and keeps ``.config`` reachable."""
+
+    def __init__(self, hf):
+        super().__init__()
+        self.hf = hf
+        self.config = hf.config
+
+    def forward(self, ids, labels=None):
+        return self.hf(input_ids=ids, labels=labels).loss
+
+    def gradient_checkpointing_enable(self):
+        self.hf.gradient_checkpointing_enable()
+
+    def save_pretrained(self, *a, **kw):
+        return self.hf.save_pretrained(*a, **kw)
+
+
+def has_weights(src):
+    """False when ``src`` is a bare config (file, or directory without weight files)."""
+    import os
+    if os.path.isfile(src):
+        return False
+    if os.path.isdir(src):
+        return any(f.endswith((".safetensors", ".bin")) for f in os.listdir(src))
+    return True  # a hub id
+
+
+def build_hf_model(args, device):
+    """``--hf-model``: pretrained weights when the path or id has any, else random
+    initialisation from its config (reference: examples/e2e_train/train.py:117-129)."""
+    from transformers import AutoConfig, AutoModelForCausalLM
+    src = args.hf_model
+    if not has_weights(src):
+        cfg = AutoConfig.from_pretrained(src)
+        if args.layers is not None:
+            cfg.num_hidden_layers = args.layers
+        cfg.use_cache = False
+        torch.manual_seed(args.seed)
+        hf = AutoModelForCausalLM.from_config(cfg, dtype=torch.bfloat16, attn_implementation="sdpa")
+    else:
+        hf = AutoModelForCausalLM.from_pretrained(src, dtype=torch.bfloat16, attn_implementation="sdpa")
+        hf.config.use_cache = False
+    model = _HFCausalLM(hf.to(torch.bfloat16).to(device))
+    model.train()
+    if args.gradient_checkpointing:
+        model.gradient_checkpointing_enable()
+    return model
+
+
 def build_model(args, device):
+    if getattr(args, "hf_model", None):
+        return build_hf_model(args, device)
     cfg = MODELS[args.model_name]()
     if args.layers is not None:
         cfg.num_layers = args.layers

@@ -7,7 +7,10 @@ The optimizer keeps an fp32 master of each quantized weight (``mode=fp32_master`
 required) and re-quantizes the packed weight from it after every step.  Pass
 ``--load-master-from <safetensors file | directory | hub id>`` to refill the master
 losslessly from the checkpoint the model was quantized from; ``--save-dir`` writes a
-plain-tensor safetensors checkpoint plus the matching HF ``quantization_config``
+plain-tensor safetensors checkpoint plus the matching HF ``quantization_config``.
+With ``--hf-model <checkpoint>`` a HuggingFace causal LM is trained, the master is
+refilled from that same checkpoint unless ``--load-master-from`` names another, and the
+export goes through ``save_quantized_pretrained`` (loadable by HF / vLLM)
 (reference: examples/qat/train.py).
 """
 
@@ -22,7 +25,7 @@ sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 import common  # noqa: E402
 from offload_adam_b200 import Adam, OffloadAdam  # noqa: E402
 from offload_adam_b200.qweight import (Int4QWeight, Int8QWeight, NF4QWeight, NVFP4QWeight,  # noqa: E402
-                                       quantize_linears)
+                                       quantize_linears, save_quantized_pretrained)
 
 QUANT = {"none": None, "int4": Int4QWeight, "int8": Int8QWeight, "nf4": NF4QWeight, "nvfp4": NVFP4QWeight}
 
@@ -65,14 +68,25 @@ def main():
                           staging_bytes=common.staging_arg(args), **hp)
     else:
         opt = Adam(model.parameters(), **hp)
-    if args.load_master_from and cls is not None:
-        missing = opt.load_master_from_pretrained(args.load_master_from, model)
-        print(f"master refilled from {args.load_master_from}; unmatched: {len(missing)}", flush=True)
+    hf = getattr(model, "hf", None)  # the HuggingFace module when --hf-model is given
+    master_from = args.load_master_from
+    if master_from is None and hf is not None and common.has_weights(args.hf_model):
+        master_from = args.hf_model  # the checkpoint from_pretrained just read
+    if master_from and cls is not None:
+        missing = opt.load_master_from_pretrained(master_from, hf if hf is not None else model)
+        print(f"master refilled from {master_from}; unmatched: {len(missing)}", flush=True)
     summary = common.train(args, model, opt, args.batch_size, device)
     summary.update(quant=args.quant, quant_group_size=args.quant_group_size,
                    quant_skip_patterns=args.quant_skip_patterns, enable_offloading=args.enable_offloading)
     common.emit(args, summary)
-    if args.save_dir is not None:
+    if args.save_dir is not None and hf is not None:
+        if hasattr(opt, "synchronize"):
+            opt.synchronize()
+        if cls is not None:
+            save_quantized_pretrained(hf, args.save_dir, cls, skip_patterns=tuple(args.quant_skip_patterns), **kw)
+        else:
+            hf.save_pretrained(args.save_dir)
+    elif args.save_dir is not None:
         from safetensors.torch import save_file
         args.save_dir.mkdir(parents=True, exist_ok=True)
         save_file({k: v.contiguous() for k, v in model.state_dict().items()}, str(args.save_dir / "model.safetensors"))

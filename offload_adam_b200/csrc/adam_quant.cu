@@ -161,10 +161,7 @@ adam_int4_push_kernel(Ptrs t, Peers pr, int64_t rows, AdamScalars s, const float
     __syncthreads();
     const int64_t left = rows - band * 32;
     const int valid = left < 32 ? (int)left : 32;
-#pragma unroll 1
-    for (int j = 0; j < q.n; ++j)
-      int4_tile_store<S>(sm, q.out_f, q.row0 + band * 32, valid, col0, q.group,
-                         reinterpret_cast<int32_t*>(q.p0[j]), reinterpret_cast<S*>(q.p1[j]));
+    int4_tile_store_multi<S, kMaxPeers>(sm, q.out_f, q.row0 + band * 32, valid, col0, q.group, q.p0, q.p1, q.n);
     __syncthreads();
   }
 }

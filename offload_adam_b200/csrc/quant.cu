@@ -275,7 +275,8 @@ int8_dequantize_kernel(const int8_t* q, const S* scales, int64_t out_f, int64_t 
       const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
       float e[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) e[i] = __fmul_rn((float)(int8_t)((w[i >> 2] >> (8 * (i & 3))) & 0xffu), s);
+      // (byte ^ 0x80) - 128 is the signed value; see small_int_to_f32
+      for (int i = 0; i < 16; ++i) e[i] = __fmul_rn(small_int_to_f32(((w[i >> 2] >> (8 * (i & 3))) & 0xffu) ^ 0x80u, 8388736.0f), s);
       Elem<S>::store16(out + v * 16, e);
     }
   } else {

@@ -190,9 +190,23 @@ __device__ __forceinline__ void nf4_unpack16(uint32_t w0, uint32_t w1, float am,
   }
 }
 
+// Round-half-even of a clamped value to an integer, and small integers back to fp32,
+// with plain fp32 additions instead of the conversion instructions (which issue at a
+// quarter of the rate): adding 1.5 * 2^23 leaves the rounded integer in the low mantissa
+// bits (two's complement for negatives), and 2^23 | k is the float 2^23 + k.  Clamping to
+// integer bounds before or after the rounding gives the same result.
+__device__ __forceinline__ int round_clamped(float x, float lo, float hi) {
+  const float t = __fadd_rn(fminf(fmaxf(x, lo), hi), 12582912.0f);
+  return (int)(__float_as_uint(t) - 0x4B400000u);
+}
+// fp32 value of k - bias for 0 <= k < 2^22
+__device__ __forceinline__ float small_int_to_f32(uint32_t k, float bias_plus_2p23) {
+  return __fsub_rn(__uint_as_float(0x4B000000u | k), bias_plus_2p23);
+}
+
 // int8: 16 values -> four words of bytes
 __device__ __forceinline__ int int8_round(float x, float inv) {
-  return (int)fminf(fmaxf(rintf(__fmul_rn(x, inv)), -128.f), 127.f);
+  return round_clamped(__fmul_rn(x, inv), -128.f, 127.f);
 }
 __device__ __forceinline__ uint4 int8_pack16(const float (&e)[16], float inv) {
   uint32_t w[4] = {0, 0, 0, 0};
@@ -203,7 +217,7 @@ __device__ __forceinline__ uint4 int8_pack16(const float (&e)[16], float inv) {
 
 // GPTQ int4: 16 values -> two words of eight (v + 8) nibbles, first value in the low nibble
 __device__ __forceinline__ int int4_round(float x, float inv) {
-  return (int)fminf(fmaxf(rintf(__fmul_rn(x, inv)), -8.f), 7.f);
+  return round_clamped(__fmul_rn(x, inv), -8.f, 7.f);
 }
 __device__ __forceinline__ void int4_pack16(const float (&e)[16], float inv, uint32_t& w0, uint32_t& w1) {
   w0 = 0; w1 = 0;
@@ -255,6 +269,34 @@ __device__ __forceinline__ void int4_tile_store(const Int4Tile& sm, int64_t out_
     if (lr < rows_valid) scales[(col0 / group + gi) * out_f + grow0 + lr] = Elem<S>::from_f32(sm.scale[gi][lr]);
   }
 }
+// The same tile into `n` replicas of the payload (own and peer GPUs'): every word is read
+// from shared memory once and its address computed once.
+template <typename S, int MAXR>
+__device__ __forceinline__ void int4_tile_store_multi(const Int4Tile& sm, int64_t out_f, int64_t grow0, int rows_valid,
+                                                      int64_t col0, int group, uint8_t* const (&p0)[MAXR],
+                                                      uint8_t* const (&p1)[MAXR], int n) {
+  for (int i = threadIdx.x; i < 16 * 32; i += blockDim.x) {
+    const int k = i >> 5, lr = i & 31;
+    if (lr < rows_valid) {
+      const int64_t at = (col0 / 8 + k) * out_f + grow0 + lr;
+      const int32_t w = sm.words[k][lr];
+#pragma unroll
+      for (int j = 0; j < MAXR; ++j)
+        if (j < n) reinterpret_cast<int32_t*>(p0[j])[at] = w;
+    }
+  }
+  const int groups_per_tile = 128 / group;
+  for (int i = threadIdx.x; i < groups_per_tile * 32; i += blockDim.x) {
+    const int gi = i >> 5, lr = i & 31;
+    if (lr < rows_valid) {
+      const int64_t at = (col0 / group + gi) * out_f + grow0 + lr;
+      const S v = Elem<S>::from_f32(sm.scale[gi][lr]);
+#pragma unroll
+      for (int j = 0; j < MAXR; ++j)
+        if (j < n) reinterpret_cast<S*>(p1[j])[at] = v;
+    }
+  }
+}
 // Loads a tile of a payload into shared memory (rows beyond rows_valid read as zero).
 template <typename S>
 __device__ __forceinline__ void int4_tile_load(Int4Tile& sm, int64_t out_f, int64_t grow0, int rows_valid,
@@ -273,8 +315,8 @@ __device__ __forceinline__ void int4_tile_load(Int4Tile& sm, int64_t out_f, int6
 __device__ __forceinline__ void int4_unpack16(uint32_t w0, uint32_t w1, float s, float (&e)[16]) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    e[i] = __fmul_rn((float)((int)((w0 >> (4 * i)) & 0xfu) - 8), s);
-    e[8 + i] = __fmul_rn((float)((int)((w1 >> (4 * i)) & 0xfu) - 8), s);
+    e[i] = __fmul_rn(small_int_to_f32((w0 >> (4 * i)) & 0xfu, 8388616.0f), s);
+    e[8 + i] = __fmul_rn(small_int_to_f32((w1 >> (4 * i)) & 0xfu, 8388616.0f), s);
   }
 }
 

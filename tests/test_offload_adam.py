@@ -297,7 +297,7 @@ def test_gpu_early_loads_and_trailing_writebacks_are_exact(pacing, clip, staging
 
     m_a, m_b = net(), net()
     o_a = OffloadAdam(m_a, transfer="staged", chunk_elems=chunk, ring_slots=3, prefetch_pacing=pacing,
-                      staging_bytes=staging_chunks * chunk * 8, **kw)
+                      staging_bytes=staging_chunks * chunk * 8, keep_resident=False, **kw)  # the ring is under test
     o_b = OffloadAdam(m_b, transfer="zero_copy", **kw)
     seen = []
     it = iter(data)
