@@ -69,6 +69,9 @@ def parse_args():
     ap.add_argument("--model-impl", choices=["own", "hf"], default="own",
                     help="this framework's arm: the package's Llama, or the HuggingFace module the reference arm trains")
     ap.add_argument("--no-resident", action="store_true", help="stream all optimizer state every step")
+    ap.add_argument("--symmetric-model", action="store_true",
+                    help="create the large parameters directly in symmetric memory (default for llama3-70b with "
+                         "more than one GPU: a second copy of the weights would not fit)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: override layer count")
     ap.add_argument("--seq", type=int, default=None)
     ap.add_argument("--ga", type=int, default=None)
@@ -176,6 +179,32 @@ def max_over_ranks(x, device):
     return t.item()
 
 
+def host_memory_shortfall(args, preset, world):
+    """None when the pinned host memory the run needs fits in what the machine has free,
+    else a one-line reason.  Per parameter element and rank: optimizer state / world (8 B
+    in fp32_master, 4 B with stochastic rounding, 6 B otherwise) plus, for the reference,
+    a full-shape bf16 gradient buffer on every rank (its host gradients are never sharded)."""
+    d = model_dims(args)
+    layer = 2 * d.hidden_size * (d.num_heads + d.num_kv_heads) * d.head_dim + 3 * d.hidden_size * d.intermediate_size
+    n = d.num_layers * layer + d.vocab_size * d.hidden_size * (1 if d.tie_embeddings else 2)
+    state = {"fp32_master": 8, "stochastic_rounding": 4}.get(preset["mode"], 6)
+    sharded = preset["optimizer"] == "distributed"
+    per_rank = n * state / (world if sharded else 1)
+    if args.impl == "reference":
+        per_rank += 2 * n
+    elif args.grad_residency == "host":
+        per_rank += 2 * n / (world if args.grad_layout == "shard" else 1)
+    need = per_rank * world
+    try:
+        avail = next(int(line.split()[1]) * 1024 for line in open("/proc/meminfo") if line.startswith("MemAvailable"))
+    except Exception:
+        return None
+    if need > 0.9 * avail:
+        return (f"needs {need / 2**30:.0f} GiB of pinned host memory on this node ({per_rank / 2**30:.0f} GiB per rank x "
+                f"{world}) but only {avail / 2**30:.0f} GiB are available")
+    return None
+
+
 # ------------------------------------------------------------------ model builders
 def model_dims(args):
     from offload_adam_b200.models.llama import llama3_8b, llama3_70b, tiny_llama
@@ -192,7 +221,10 @@ def build_ours(args, preset, device):
     if args.model_impl == "hf":
         model, _ = build_hf_llama(args, preset, device)
     else:
-        model = build_llama(cfg, device=device, dtype=torch.bfloat16, seed=0)
+        symmetric = (args.symmetric_model or args.model == "llama3-70b") and dist.get_world_size() > 1 \
+            and args.comm != "nccl"
+        model = build_llama(cfg, device=device, dtype=torch.bfloat16, seed=0,
+                            symmetric_group=dist.group.WORLD if symmetric else None)
         model.train()
         if args.grad_ckpt:
             model.gradient_checkpointing_enable()
@@ -372,6 +404,15 @@ def main():
     torch.backends.cuda.matmul.allow_tf32 = True
     torch.backends.cudnn.allow_tf32 = True
 
+    short = host_memory_shortfall(args, preset, world)
+    if short is not None:
+        # pinning more host memory than the machine has takes the whole node down: refuse
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "unavailable": short,
+                              "config": {"model": args.model, "grad_layout": args.grad_layout, "n_gpus": world}}))
+        dist.barrier()
+        dist.destroy_process_group()
+        return 0
     build = build_ours if args.impl == "ours" else build_reference
     t_build = time.perf_counter()
     model, opt, loss_fn, vocab = build(args, preset, device)

@@ -257,18 +257,33 @@ class LlamaForCausalLM(nn.Module):
                                             shift.reshape(-1), self.config.ce_chunk)
 
 
-def build_llama(cfg: LlamaConfig, device="cuda", dtype=torch.bfloat16, seed=0) -> LlamaForCausalLM:
+def build_llama(cfg: LlamaConfig, device="cuda", dtype=torch.bfloat16, seed=0, symmetric_group=None,
+                symmetric_threshold=1024 * 1024) -> LlamaForCausalLM:
     """Random-init model (N(0, init_std), norms at 1) created directly on ``device`` and
     directly in ``dtype``: no fp32 copy of the weights ever exists (a 70B model would not
-    fit otherwise)."""
+    fit otherwise).  With ``symmetric_group`` (a process group) the large parameters are
+    created in symmetric memory, where the peer-memory path of ``DistributedOffloadAdam``
+    wants them, so that no second copy of the weights is needed when the optimizer is
+    built (``parallel.symm.materialize_in_symmetric_memory``)."""
     gen_state = torch.random.get_rng_state()
     default_dtype = torch.get_default_dtype()
     torch.manual_seed(seed)
     try:
         torch.set_default_dtype(dtype)
-        with torch.device(device):
-            model = LlamaForCausalLM(cfg)
-        model = model.to(dtype)
+        if symmetric_group is None:
+            with torch.device(device):
+                model = LlamaForCausalLM(cfg)
+            model = model.to(dtype)
+        else:
+            from ..parallel.symm import materialize_in_symmetric_memory
+            with torch.device("meta"):
+                model = LlamaForCausalLM(cfg)
+            materialize_in_symmetric_memory(model, device, symmetric_group, symmetric_threshold, dtype)
+            with torch.no_grad():
+                for p in model.parameters():
+                    if p.dim() == 1:
+                        p.fill_(1.0)  # norm weights
+                model.reset_parameters()
     finally:
         torch.set_default_dtype(default_dtype)
         torch.random.set_rng_state(gen_state)

@@ -66,6 +66,56 @@ def _nbytes(t):
     return t.numel() * t.element_size()
 
 
+def materialize_in_symmetric_memory(model, device, group=None, threshold=1024 * 1024, dtype=torch.bfloat16):
+    """Give a model that was built on the ``meta`` device its storage, with every large
+    parameter placed directly in a symmetric allocation.
+
+    ``SymmZero1`` keeps the parameters of the peer-memory path in symmetric memory; a model
+    that already exists in ordinary device memory is copied there, so for a moment both
+    copies are alive.  A model whose weights fill most of the GPU (70B in bf16 is 141 GB of
+    180) cannot afford that: build it with ``torch.device('meta')``, call this function, then
+    initialise or load the weights and construct ``DistributedOffloadAdam(model,
+    comm='symm', inplace_param_threshold=threshold)``, which recognises the allocation and
+    adopts it.  Parameters with fewer than ``threshold`` elements get ordinary tensors (they
+    are the ones the optimizer keeps on the GPU).  The contents are uninitialised.
+    Collective: every rank of ``group`` must call it with the same model."""
+    import os
+
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    import torch.distributed._symmetric_memory as symm_mem
+
+    group = group if group is not None else dist.group.WORLD
+    seen, offsets, total = {}, {}, 0
+    owners = []
+    for module in model.modules():
+        for name, p in list(module.named_parameters(recurse=False)):
+            owners.append((module, name, p))
+            if id(p) in seen or p.numel() < threshold:
+                continue
+            seen[id(p)] = p
+            offsets[id(p)] = total
+            total += _round_up(p.numel() * 2, _ALIGN)
+    arena = symm_mem.empty(max(total, _ALIGN), dtype=torch.uint8, device=device)
+    handle = symm_mem.rendezvous(arena, group)
+    new = {}
+    for module, name, p in owners:
+        if id(p) not in new:
+            if id(p) in offsets:
+                o = offsets[id(p)]
+                data = arena[o: o + p.numel() * 2].view(dtype).view(p.shape)
+            else:
+                data = torch.empty(p.shape, dtype=dtype, device=device)
+            new[id(p)] = torch.nn.Parameter(data, requires_grad=p.requires_grad)
+        setattr(module, name, new[id(p)])  # shared (tied) parameters stay shared
+    for module in model.modules():
+        for name, b in list(module.named_buffers(recurse=False)):
+            if b is not None and b.is_meta:
+                setattr(module, name, torch.empty(b.shape, dtype=b.dtype, device=device))
+    model._oab_symmetric_params = {"arena": arena, "handle": handle, "group": group,
+                                   "offsets": {id(new[k]): v for k, v in offsets.items()}}
+    return model
+
+
 class SymmZero1:
     def __init__(self, opt, model, timeout_ms=30000):
         import os
@@ -147,12 +197,19 @@ class SymmZero1:
         ctrl_bytes = self.small_off_bytes + self.small_bytes
 
         # ---- symmetric allocations + rendezvous
-        self.param_arena = symm_mem.empty(max(ptotal, _ALIGN), dtype=torch.uint8, device=self.dev)
+        # a model materialised by materialize_in_symmetric_memory already lives in an
+        # allocation of exactly this layout: adopt it instead of copying the parameters
+        pre = getattr(model, "_oab_symmetric_params", None)
+        adopted = (pre is not None and pre["group"] is group and pre["arena"].numel() >= max(ptotal, _ALIGN)
+                   and not any(self.is_quant.values())
+                   and all(pre["offsets"].get(id(p)) == self.poff[p] for p in self.params))
+        self.param_arena = pre["arena"] if adopted else \
+            symm_mem.empty(max(ptotal, _ALIGN), dtype=torch.uint8, device=self.dev)
         self.grad_arena = symm_mem.empty(max(gtotal, _ALIGN), dtype=torch.uint8, device=self.dev)
         self.ctrl = symm_mem.empty(ctrl_bytes, dtype=torch.uint8, device=self.dev)
         self.ctrl.zero_()
         self.grad_arena.zero_()
-        self.h_param = symm_mem.rendezvous(self.param_arena, group)
+        self.h_param = pre["handle"] if adopted else symm_mem.rendezvous(self.param_arena, group)
         self.h_grad = symm_mem.rendezvous(self.grad_arena, group)
         self.h_ctrl = symm_mem.rendezvous(self.ctrl, group)
         self.param_base = [int(x) for x in self.h_param.buffer_ptrs]
@@ -179,7 +236,7 @@ class SymmZero1:
                     home = self.param_arena[o: o + _nbytes(t)].view(t.dtype).view(t.shape)
                     home.copy_(t)
                     setattr(p, name, home)  # p.data is rebuilt from these attributes on every access
-            else:
+            elif not adopted:
                 o, n = self.poff[p], p.numel()
                 home = self.param_arena[o: o + n * 2].view(torch.bfloat16).view(p.shape)
                 home.copy_(p.data)
@@ -187,6 +244,7 @@ class SymmZero1:
             if p in self.goff:
                 o, n = self.goff[p], p.numel()
                 self.grad_view[p] = self.grad_arena[o: o + n * 2].view(torch.bfloat16).view(p.shape)
+        self.adopted_param_arena = adopted
         self.acc_valid = {p: False for p in self.params}
         torch.cuda.empty_cache()  # the parameters' old storage goes back to the driver
         self.shard_bytes = {p: (p.numel() // N if self.is_sharded[p] else p.numel()) * 2 for p in self.params}
