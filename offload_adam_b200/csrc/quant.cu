@@ -289,10 +289,9 @@ int8_dequantize_kernel(const int8_t* q, const S* scales, int64_t out_f, int64_t 
 // Tile = 32 rows x 128 columns (see Int4Tile): every thread moves 16 consecutive
 // elements of a row with one (bf16/fp16) or two (fp32) 256-bit accesses; the packed
 // words are transposed through shared memory.
-// A CTA works on TILES neighbouring tiles of one 32-row band, all of their loads issued
-// before the first use.  Measured on B200: de-quantization (few registers, latency of
-// the transposed loads exposed) gains from four tiles, quantization is fastest with one.
-constexpr int kInt4QuantTiles = 1, kInt4DequantTiles = 4;
+// A CTA can work on several neighbouring tiles of one 32-row band, all of their loads issued
+// before the first use; measured on B200, quantization is fastest with one.
+constexpr int kInt4QuantTiles = 1;
 
 template <typename T, typename S, int kInt4Tiles>
 __global__ void __launch_bounds__(kThreads)
@@ -321,27 +320,33 @@ int4_quantize_kernel(const T* x, int64_t out_f, int64_t in_f, int group, int32_t
     if (tile0 + t < ntiles) int4_tile_store<S>(sm[t], out_f, row0, valid, (tile0 + t) << 7, group, qweight, scales);
 }
 
-template <typename S, int kInt4Tiles>
+// De-quantization without shared memory: a warp takes 32 consecutive output rows, one per
+// lane.  Word k of the transposed payload is then a coalesced 128-byte read across the
+// lanes, and a lane that has read eight consecutive words owns 64 consecutive outputs of
+// its row: a whole 128-byte line, written with four 256-bit stores.  Nothing is exchanged
+// between threads, so there is no barrier and eight loads per lane are in flight at once.
+// The warps of a CTA share the band and split its columns.
+template <typename S>
 __global__ void __launch_bounds__(kThreads)
 int4_dequantize_kernel(const int32_t* qweight, const S* scales, int64_t out_f, int64_t in_f, int group, S* out, int aligned) {
-  __shared__ Int4Tile sm[kInt4Tiles];
-  const int64_t row0 = (int64_t)blockIdx.x * 32;
-  const int64_t tile0 = (int64_t)blockIdx.y * kInt4Tiles, ntiles = in_f >> 7;
-  const int64_t left = out_f - row0;
-  const int valid = left < 32 ? (int)left : 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row = (int64_t)blockIdx.x * 32 + lane;
+  if (row >= out_f) return;
+  const int64_t spans = in_f >> 6;  // 64 columns = 8 words per step
+  for (int64_t sp = (int64_t)blockIdx.y * (kThreads / 32) + warp; sp < spans; sp += (int64_t)gridDim.y * (kThreads / 32)) {
+    uint32_t w[8];
 #pragma unroll
-  for (int t = 0; t < kInt4Tiles; ++t)
-    if (tile0 + t < ntiles) int4_tile_load<S>(sm[t], out_f, row0, valid, (tile0 + t) << 7, group, qweight, scales);
-  __syncthreads();
-  const int lr = threadIdx.x >> 3, seg = threadIdx.x & 7;
-  if (row0 + lr >= out_f) return;
+    for (int k = 0; k < 8; ++k) w[k] = (uint32_t)qweight[(sp * 8 + k) * out_f + row];
+    const int64_t col = sp << 6;
+    S* dst = out + row * in_f + col;
 #pragma unroll
-  for (int t = 0; t < kInt4Tiles; ++t) {
-    if (tile0 + t >= ntiles) break;
-    float e[16];
-    int4_unpack16((uint32_t)sm[t].words[seg * 2][lr], (uint32_t)sm[t].words[seg * 2 + 1][lr],
-                  sm[t].scale[(seg * 16) / group][lr], e);
-    store16_any(out + (row0 + lr) * in_f + ((tile0 + t) << 7) + seg * 16, e, aligned != 0);
+    for (int h = 0; h < 4; ++h) {
+      // 16 columns never straddle a group (groups are 32, 64 or 128 columns wide)
+      const float s = Elem<S>::to_f32(scales[((col + h * 16) / group) * out_f + row]);
+      float e[16];
+      int4_unpack16(w[2 * h], w[2 * h + 1], s, e);
+      store16_any(dst + h * 16, e, aligned != 0);
+    }
   }
 }
 
@@ -489,9 +494,14 @@ cudaError_t launch_int4_dequantize(const int32_t* qweight, const void* scales, i
                                    int64_t in_f, int group, void* out, cudaStream_t st) {
   if (out_f <= 0) return cudaSuccess;
   if (in_f % 128 != 0 || (group != 32 && group != 64 && group != 128)) return cudaErrorInvalidValue;
-  dim3 grid((unsigned)((out_f + 31) / 32), (unsigned)((in_f / 128 + kInt4DequantTiles - 1) / kInt4DequantTiles));
+  // one CTA per band of 32 rows unless there are few bands: then the columns are split over grid.y
+  const int64_t bands = (out_f + 31) / 32, spans = in_f / 64;
+  int64_t gy = (kNumSMs * 4 + bands - 1) / bands;
+  if (gy > (spans + 7) / 8) gy = (spans + 7) / 8;
+  if (gy < 1) gy = 1;
+  dim3 grid((unsigned)bands, (unsigned)gy);
   count_launch();
-  OAB_DISPATCH_SCALE(scale_dtype, int4_dequantize_kernel<S, kInt4DequantTiles><<<grid, kThreads, 0, st>>>(qweight, (const S*)scales, out_f, in_f, group, (S*)out, aligned32(out) ? 1 : 0));
+  OAB_DISPATCH_SCALE(scale_dtype, int4_dequantize_kernel<S><<<grid, kThreads, 0, st>>>(qweight, (const S*)scales, out_f, in_f, group, (S*)out, aligned32(out) ? 1 : 0));
   return cudaGetLastError();
 }
 

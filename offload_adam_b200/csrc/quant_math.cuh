@@ -204,27 +204,37 @@ __device__ __forceinline__ float small_int_to_f32(uint32_t k, float bias_plus_2p
   return __fsub_rn(__uint_as_float(0x4B000000u | k), bias_plus_2p23);
 }
 
-// int8: 16 values -> four words of bytes
+// int8: 16 values -> four words of bytes.  The magic constant carries the +128 bias, so the
+// low byte of the sum is q + 128; flipping bit 7 of every byte gives two's complement q.
 __device__ __forceinline__ int int8_round(float x, float inv) {
   return round_clamped(__fmul_rn(x, inv), -128.f, 127.f);
+}
+__device__ __forceinline__ uint32_t int8_biased(float x, float inv) {
+  const float t = __fadd_rn(fminf(fmaxf(__fmul_rn(x, inv), -128.f), 127.f), 12583040.0f);  // 1.5 * 2^23 + 128
+  return __float_as_uint(t) & 0xffu;
 }
 __device__ __forceinline__ uint4 int8_pack16(const float (&e)[16], float inv) {
   uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
-  for (int i = 0; i < 16; ++i) w[i >> 2] |= ((uint32_t)(uint8_t)(int8_t)int8_round(e[i], inv)) << (8 * (i & 3));
-  return make_uint4(w[0], w[1], w[2], w[3]);
+  for (int i = 0; i < 16; ++i) w[i >> 2] |= int8_biased(e[i], inv) << (8 * (i & 3));
+  return make_uint4(w[0] ^ 0x80808080u, w[1] ^ 0x80808080u, w[2] ^ 0x80808080u, w[3] ^ 0x80808080u);
 }
 
-// GPTQ int4: 16 values -> two words of eight (v + 8) nibbles, first value in the low nibble
+// GPTQ int4: 16 values -> two words of eight (v + 8) nibbles, first value in the low nibble.
+// Here the magic constant carries the +8, so the low nibble of the sum is the stored code.
 __device__ __forceinline__ int int4_round(float x, float inv) {
   return round_clamped(__fmul_rn(x, inv), -8.f, 7.f);
+}
+__device__ __forceinline__ uint32_t int4_code(float x, float inv) {
+  const float t = __fadd_rn(fminf(fmaxf(__fmul_rn(x, inv), -8.f), 7.f), 12582920.0f);  // 1.5 * 2^23 + 8
+  return __float_as_uint(t) & 0xfu;
 }
 __device__ __forceinline__ void int4_pack16(const float (&e)[16], float inv, uint32_t& w0, uint32_t& w1) {
   w0 = 0; w1 = 0;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    w0 |= ((uint32_t)(int4_round(e[i], inv) + 8) & 0xfu) << (4 * i);
-    w1 |= ((uint32_t)(int4_round(e[8 + i], inv) + 8) & 0xfu) << (4 * i);
+    w0 |= int4_code(e[i], inv) << (4 * i);
+    w1 |= int4_code(e[8 + i], inv) << (4 * i);
   }
 }
 // scale of a symmetric int group from its absolute maximum: the stored scale is the fp32
