@@ -33,7 +33,10 @@ extern "C" {
 //   n       0 <= n <= OAB_SUMSQ_STATIC_MAX_ELEMS; larger inputs are refused with
 //           OAB_STATIC_TOO_LARGE and nothing is launched
 //   out     device pointer to one float, overwritten
-//   stream  cudaStream_t on which the work is enqueued (NULL: default stream)
+//   stream  cudaStream_t on which the work is enqueued (NULL: default stream).  It has
+//           to belong to the device that is current in the calling thread, which is also
+//           the device x and out live on: with a stream of another device the memset or
+//           the launch fails and the call returns OAB_STATIC_CUDA_ERROR
 //   err     optional buffer that receives a readable message on failure
 //   err_len size of that buffer in bytes
 //
