@@ -395,3 +395,49 @@ def test_parameter_without_gradient_does_not_stall_the_peer_path():
         mp.spawn(_unused_worker, args=(2, free_port(), d), nprocs=2, join=True)
         reports = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(2)]
     assert all(r["ok"] for r in reports), reports
+
+
+# ----------------------- a model created directly in symmetric memory is adopted, not copied
+def _adopt_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    report = {"ok": False}
+    try:
+        from offload_adam_b200 import DistributedOffloadAdam
+        from offload_adam_b200.models.llama import build_llama, tiny_llama
+        cfg = tiny_llama()
+        plain = build_llama(cfg, device=device, seed=0)
+        symm = build_llama(cfg, device=device, seed=0, symmetric_group=dist.group.WORLD, symmetric_threshold=1000)
+        symm.load_state_dict(plain.state_dict())
+        kw = dict(lr=1e-3, mode="fp32_master", max_grad_norm=1.0, comm="symm", grad_layout="shard",
+                  inplace_param_threshold=1000, wait_timeout_ms=20000, chunk_elems=16384)
+        o_plain = DistributedOffloadAdam(plain, **kw)
+        o_symm = DistributedOffloadAdam(symm, **kw)
+        assert o_symm._symm.adopted_param_arena and not o_plain._symm.adopted_param_arena
+        g = torch.Generator().manual_seed(50 + rank)
+        for _ in range(2):
+            for micro in range(2):
+                ids = torch.randint(0, cfg.vocab_size, (2, 64), generator=g).to(device)
+                for model, opt in ((plain, o_plain), (symm, o_symm)):
+                    opt.ready_for_optimizer_step = micro == 1
+                    (model(ids, labels=ids) / 2).backward()
+            o_plain.step()
+            o_symm.step()
+        o_plain.synchronize()
+        o_symm.synchronize()
+        assert all(torch.equal(a, b) for a, b in zip(plain.parameters(), symm.parameters()))
+        report["ok"] = True
+    finally:
+        torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
+        dist.destroy_process_group()
+
+
+def test_model_built_in_symmetric_memory_is_adopted():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_adopt_worker, args=(2, free_port(), d), nprocs=2, join=True)
+        reports = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(2)]
+    assert all(r["ok"] for r in reports), reports
