@@ -459,7 +459,8 @@ def main():
     peak_gb = torch.cuda.max_memory_allocated() / 1024**3
 
     if args.verbose > 2 and args.impl == "ours" and rank == 0:
-        print("[rank 0] last timed step, ms from its start:", opt.trace_report(), flush=True)
+        print("[rank 0] last timed step, ms from its start:", opt.trace_report(),
+              "host:", getattr(opt, "host_trace", None), flush=True)
     if args.profile_range:
         torch.cuda.synchronize()
         torch.cuda.profiler.start()

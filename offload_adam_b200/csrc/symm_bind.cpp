@@ -66,6 +66,15 @@ void signal(const std::vector<int64_t>& ptrs, int64_t value, int64_t stream) {
   ok(oab::launch_signal(p, (int)ptrs.size(), (uint32_t)value, pick(stream)), "signal");
 }
 
+void signal_many(const std::vector<int64_t>& bases, int64_t first, int64_t stride, int64_t count, int64_t value,
+                 int64_t stream) {
+  TORCH_CHECK(bases.size() <= (size_t)oab::kMaxPeers, "at most 8 targets");
+  uint32_t* p[oab::kMaxPeers] = {};
+  for (size_t j = 0; j < bases.size(); ++j) p[j] = reinterpret_cast<uint32_t*>(bases[j]);
+  ok(oab::launch_signal_many(p, (int)bases.size(), (int)first, (int)stride, (int)count, (uint32_t)value, pick(stream)),
+     "signal_many");
+}
+
 void scalar_exchange(const Tensor& my_value, const std::vector<int64_t>& peer_slots,
                      const std::vector<int64_t>& peer_flags, const Tensor& local_slots,
                      const Tensor& local_flags, int64_t rank, int64_t epoch, double timeout_ms,
@@ -108,6 +117,8 @@ void bind_symm(py::module_& m) {
   m.def("wait_flags", &wait_flags, py::arg("flags"), py::arg("offset"), py::arg("n"), py::arg("epoch"),
         py::arg("timeout_ms"), py::arg("status"), py::arg("code"), py::arg("stream") = 0);
   m.def("signal", &signal, py::arg("ptrs"), py::arg("value"), py::arg("stream") = 0);
+  m.def("signal_many", &signal_many, py::arg("bases"), py::arg("first"), py::arg("stride"), py::arg("count"),
+        py::arg("value"), py::arg("stream") = 0);
   m.def("scalar_exchange", &scalar_exchange, py::arg("my_value"), py::arg("peer_slots"),
         py::arg("peer_flags"), py::arg("local_slots"), py::arg("local_flags"), py::arg("rank"),
         py::arg("epoch"), py::arg("timeout_ms"), py::arg("status"), py::arg("out"), py::arg("stream") = 0,

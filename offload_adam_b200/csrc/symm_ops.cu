@@ -139,6 +139,13 @@ __global__ void signal_kernel(SignalPtrs sp, int n, uint32_t value) {
   if ((int)threadIdx.x < n) st_release_sys(sp.p[threadIdx.x], value);
 }
 
+// the same for `count` flag words at base + first + i * stride in every peer's flag array
+__global__ void signal_many_kernel(SignalPtrs bases, int n_peers, int first, int stride, int count, uint32_t value) {
+  __threadfence_system();
+  for (int i = threadIdx.x; i < count; i += blockDim.x)
+    for (int j = 0; j < n_peers; ++j) st_release_sys(bases.p[j] + first + (int64_t)i * stride, value);
+}
+
 __global__ void mirror_words_kernel(const int* src, int* dst, int n) {
   // plain stores (to mapped host memory): keeps the DMA engines out of it
   if ((int)threadIdx.x < n) dst[threadIdx.x] = src[threadIdx.x];
@@ -228,6 +235,17 @@ cudaError_t launch_signal(uint32_t* const* ptrs_host, int n, uint32_t value, cud
   for (int j = 0; j < kMaxPeers; ++j) sp.p[j] = ptrs_host[j < n ? j : 0];
   count_launch();
   signal_kernel<<<1, 32, 0, stream>>>(sp, n, value);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_signal_many(uint32_t* const* bases_host, int n_peers, int first, int stride, int count,
+                               uint32_t value, cudaStream_t stream) {
+  if (count <= 0 || n_peers <= 0) return cudaSuccess;
+  if (n_peers > kMaxPeers) return cudaErrorInvalidValue;
+  SignalPtrs sp;
+  for (int j = 0; j < kMaxPeers; ++j) sp.p[j] = bases_host[j < n_peers ? j : 0];
+  count_launch();
+  signal_many_kernel<<<1, 256, 0, stream>>>(sp, n_peers, first, stride, count, value);
   return cudaGetLastError();
 }
 

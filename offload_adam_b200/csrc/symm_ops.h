@@ -46,6 +46,11 @@ cudaError_t launch_wait_flags(const uint32_t* flags, int n, uint32_t epoch, uint
 // to each of the n addresses (flag words in the peers' memory).
 cudaError_t launch_signal(uint32_t* const* ptrs_host, int n, uint32_t value, cudaStream_t stream);
 
+// As launch_signal for many flags at once: word first + i * stride (i < count) of the flag
+// array at bases_host[j] on every one of the n_peers ranks receives `value`.
+cudaError_t launch_signal_many(uint32_t* const* bases_host, int n_peers, int first, int stride, int count,
+                               uint32_t value, cudaStream_t stream);
+
 // dst[i] = src[i] for i < n <= 32, done by a kernel so that a status word can be
 // mirrored into mapped host memory without queueing behind bulk DMA copies.
 cudaError_t launch_mirror_words(const int* src, int* dst, int n, cudaStream_t stream);

@@ -300,7 +300,7 @@ class TransferEngine:
     # ------------------------------------------------------------------- step
     def step(self, pid, param, dev_grad, host_grad, states, hp, step, decoupled, clip=None, seed=0,
              amax=None, fork=True, g_peers=None, g_scale=1.0, p_peers=None, status=None, quant=None,
-             chunk=0, master_copy=None):
+             chunk=0, master_copy=None, retain=True):
         """Adam step of one offloaded tensor (or shard).
 
         ``states`` holds the host tensors ``exp_avg``, ``exp_avg_sq`` and, by mode,
@@ -346,7 +346,8 @@ class TransferEngine:
                 stream=self.opt_stream.cuda_stream if self.cuda else 0,
                 use_cuda=self.cuda, g_peers=g_peers, g_scale=g_scale, p_peers=p_peers, status=status,
             )
-        self._retain(dev_grad)
+        if retain:
+            self._retain(dev_grad)
         if self.serialize:
             self.synchronize()
         return where

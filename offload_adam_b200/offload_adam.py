@@ -35,6 +35,7 @@ from __future__ import annotations
 
 import os
 import random
+import time
 import warnings
 
 import torch
@@ -580,12 +581,19 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
     def _after_param_update(self, p):
         """Hook for subclasses (e.g. all-gather of an updated shard)."""
 
+    def _grad_is_persistent(self, p):
+        """True when the gradient handed to the step lives in a buffer the optimizer owns for
+        good (nothing to keep alive, nothing to count against the gradient budget)."""
+        return False
+
     def _step_extra(self, p):
         """Extra keyword arguments of ``TransferEngine.step`` (peer addresses)."""
         return {}
 
-    def _step_offload(self, p, group, clip_coef=None, dev_grad=None):
-        """Enqueue the step of one offloaded parameter on the side streams."""
+    def _step_offload(self, p, group, clip_coef=None, dev_grad=None, fork=True):
+        """Enqueue the step of one offloaded parameter on the side streams.  ``fork=False``:
+        the optimizer stream is already ordered after the main stream (the caller forked it
+        and has put nothing on the main stream since)."""
         st = self.state[p]
         st["step"] += 1
         self._step_dirty = True
@@ -603,11 +611,12 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         quant = p in self._quant_params
         if quant:
             self._warn_lossy_master_once(st)
-            self._step_quant(p, group, st, dev_grad, host_grad, clip_coef)
+            self._step_quant(p, group, st, dev_grad, host_grad, clip_coef, fork=fork)
         else:
             self._engine.step(self._pid[p], self._param_view(p), dev_grad, host_grad, states,
                               self._hp(group), st["step"], self.decoupled_weight_decay,
-                              clip=clip_coef, seed=seed, **extra)
+                              clip=clip_coef, seed=seed, fork=fork,
+                              retain=not self._grad_is_persistent(p), **extra)
         st["host_grad_valid"] = False
         self._after_param_update(p)
 
@@ -671,7 +680,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
     def _combine_amax(self, p, plan):
         """Hook for subclasses: turn the local max|master| into the whole weight's."""
 
-    def _step_quant(self, p, group, st, dev_grad, host_grad, clip_coef):
+    def _step_quant(self, p, group, st, dev_grad, host_grad, clip_coef, fork=True):
         """Quantized parameter on the fused route: the fp32 master and the moments stream
         through the staging buffer like any dense tensor; each chunk is a number of whole
         rows, and the kernel that updates them also re-quantizes them and stores the packed
@@ -692,7 +701,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             tmp = self._master_tmp
         where = eng.step(self._pid[p], None, dev_grad, host_grad, states, self._hp(group), st["step"],
                          self.decoupled_weight_decay, clip=clip_coef, amax=plan["local_amax"],
-                         quant=plan["spec"], chunk=plan["chunk"], master_copy=tmp, **extra)
+                         quant=plan["spec"], chunk=plan["chunk"], master_copy=tmp, fork=fork,
+                         retain=not self._grad_is_persistent(p), **extra)
         if plan["nvfp4"]:
             # second pass: the tensor scale needs max|master| of the whole updated weight
             self._combine_amax(p, plan)
@@ -870,13 +880,18 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         if trace:
             eng.mark("clip_coef_done")
         inplace = []
+        # one fork serves the whole loop: nothing lands on the main stream inside it
+        self._engine.fork_from_main()
+        host_t = [time.perf_counter()] if trace else None
         for group in self.param_groups:
             for p in group["params"]:
                 if p in self._inplace_params:
                     self.state[p]["step"] += 1
                     inplace.append(p)
                 else:
-                    self._step_offload(p, group, clip_coef=clip)
+                    self._step_offload(p, group, clip_coef=clip, fork=False)
+        if trace:
+            host_t.append(time.perf_counter())
         self._step_inplace_batch(inplace, clip_coef=clip)
         if trace:
             eng.mark("kernels_done", "opt")
@@ -885,6 +900,9 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         self._finish_step()
         if trace:
             eng.mark("step_end")
+            host_t.append(time.perf_counter())
+            self.host_trace = {"enqueue_all_tensors_ms": round((host_t[1] - host_t[0]) * 1e3, 2),
+                               "small_tensors_and_finish_ms": round((host_t[2] - host_t[1]) * 1e3, 2)}
         if self.max_grad_norm is not None:
             torch.sqrt(self._normsq, out=self._norms)
             self._normsq.zero_()

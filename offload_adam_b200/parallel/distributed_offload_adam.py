@@ -372,9 +372,14 @@ class DistributedOffloadAdam(OffloadAdam):
             return None  # rows divided among ranks, no peer mappings: the collective route below
         return super()._fused_quant_plan(p)
 
-    def _step_quant(self, p, group, st, dev_grad, host_grad, clip_coef):
+    def _grad_is_persistent(self, p):
+        # the reduced slices of the clip path and the shard accumulators are buffers of the
+        # symmetric-memory path, alive as long as the optimizer
+        return self._symm is not None and self._symm.handles(p) and p in self._symm.red
+
+    def _step_quant(self, p, group, st, dev_grad, host_grad, clip_coef, fork=True):
         if p not in self._sharded or self._fused_quant_plan(p) is not None:
-            return super()._step_quant(p, group, st, dev_grad, host_grad, clip_coef)
+            return super()._step_quant(p, group, st, dev_grad, host_grad, clip_coef, fork=fork)
         # sharded quantized parameter over torch.distributed: the owner of each row range
         # updates its master slice, quantizes those rows and the PACKED rows are gathered
         # (at most one byte per element on the wire instead of four, and no replica

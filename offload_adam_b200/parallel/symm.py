@@ -279,7 +279,7 @@ class SymmZero1:
         self.total_sq = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.epoch = 1
         self.xseq = [1, 1]   # sequence numbers of the scalar exchanges: main stream, optimizer stream
-        self._signaled = set()
+        self._params_signaled = False
         # norm slots counted by this rank: its slices of sharded tensors, plus (rank 0
         # only) everything that is identical on all ranks
         idx = [opt._pid[p] for p in opt._all_params
@@ -392,9 +392,9 @@ class SymmZero1:
         return kw
 
     def after_param_update(self, p):
-        i = self.index[p]
-        self._signaled.add(p)
-        self.C.signal(self._flag_ptrs(self.F_PARAM, i * self.N + self.rank), self.epoch, self._opt_stream())
+        """The rows of ``p`` are in every replica once the kernels enqueued so far have run; the
+        flags of all tensors are raised together at the end of the step (``before_finish``):
+        nobody waits for a single tensor, and one launch replaces one per tensor."""
 
     # ------------------------------------------------------------ scalar exchanges
     def _exchange(self, value, out, on_opt_stream, op_max):
@@ -447,17 +447,21 @@ class SymmZero1:
     def before_finish(self):
         if self.opt._pending_inplace:
             self.reduce_small_bucket()
+        if self.params and self.opt._step_dirty:
+            # every parameter kernel of this step is on the optimizer stream by now: raise this
+            # rank's flag of every tensor on every rank (a tensor that got no gradient was not
+            # stepped on any rank; its flag goes up with the others so that nobody waits for it)
+            self.C.signal_many([b for b in self.ctrl_base], self.F_PARAM + self.rank, self.N, len(self.params),
+                               self.epoch, self._opt_stream())
+            self._params_signaled = True
 
     def after_finish(self):
         """End of a step; the main stream is already ordered after the optimizer stream."""
         C, N = self.C, self.N
         if self.params:
-            # a tensor that received no gradient this step was not stepped (on any rank:
-            # the ranks run the same model); raise its flag so that nobody waits for it
-            for p in self.params:
-                if p not in self._signaled:
-                    C.signal(self._flag_ptrs(self.F_PARAM, self.index[p] * N + self.rank), self.epoch)
-            self._signaled.clear()
+            if not self._params_signaled:  # only small parameters were stepped
+                C.signal_many([b for b in self.ctrl_base], self.F_PARAM + self.rank, N, len(self.params), self.epoch)
+            self._params_signaled = False
             C.wait_flags(self.flags, self.F_PARAM, len(self.params) * N, self.epoch, self.timeout_ms,
                          self.status, C.SYMM_TIMEOUT_PARAM)
         if self.small and self.small_reduced_epoch == self.epoch:
