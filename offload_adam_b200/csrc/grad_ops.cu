@@ -137,4 +137,18 @@ cudaError_t launch_clip_finalize(const float* slots, const int* index, int n, co
   return cudaGetLastError();
 }
 
+namespace {
+__global__ void check_canary_kernel(const uint32_t* guard, int words, int* status, int tag) {
+  for (int i = threadIdx.x; i < words; i += blockDim.x)
+    if (guard[i] != kCanaryWord && atomicCAS(status, 0, 1) == 0) status[1] = tag;
+}
+}  // namespace
+
+cudaError_t launch_check_canary(const void* guard, int words, int* status, int tag, cudaStream_t stream) {
+  if (guard == nullptr || status == nullptr || words <= 0) return cudaErrorInvalidValue;
+  count_launch();
+  check_canary_kernel<<<1, 64, 0, stream>>>(static_cast<const uint32_t*>(guard), words, status, tag);
+  return cudaGetLastError();
+}
+
 }  // namespace oab

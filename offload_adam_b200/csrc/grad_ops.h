@@ -31,4 +31,9 @@ cudaError_t launch_clip_finalize(const float* slots, const int* index, int n, co
                                  float max_norm, float* coef_norm, float* total_sq_out,
                                  cudaStream_t stream);
 
+// Debugging aid: compares `words` 32-bit words at `guard` with kCanaryWord and, on the first
+// mismatch, stores {1, tag} into status[0..1] (device memory; first failure wins).  Never traps.
+constexpr uint32_t kCanaryWord = 0xA5A5A5A5u;
+cudaError_t launch_check_canary(const void* guard, int words, int* status, int tag, cudaStream_t stream);
+
 }  // namespace oab

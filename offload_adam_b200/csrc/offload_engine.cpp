@@ -22,7 +22,8 @@ size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 size_t OffloadEngine::min_ring_bytes(int64_t chunk_elems) {
   // three full-width chunks (g, m, v, fp32 extra) so that load, compute and
   // write-back of consecutive chunks overlap
-  return 3 * (up256(2 * chunk_elems) * 3 + up256(4 * chunk_elems));
+  // (+ room for the guard words of the debugging option and its status block)
+  return 3 * (up256(2 * chunk_elems) * 3 + up256(4 * chunk_elems)) + 8 * 256;
 }
 
 void OffloadEngine::check(cudaError_t e, const char* what) {
@@ -43,6 +44,13 @@ OffloadEngine::OffloadEngine(int device, cudaStream_t compute, cudaStream_t h2d,
     throw std::invalid_argument("OffloadEngine: staging buffer must be 256-byte aligned");
   ring_ = static_cast<char*>(workspace);
   ring_bytes_ = ws_bytes / 256 * 256;
+  if (opt_.canaries) {
+    if (ring_bytes_ < min_ring_bytes(opt_.chunk_elems) + 4 * kGuardBytes)
+      throw std::invalid_argument("OffloadEngine: staging buffer too small for canaries");
+    ring_bytes_ -= 256;
+    canary_status_ = reinterpret_cast<int*>(ring_ + ring_bytes_);
+    check(cudaMemsetAsync(canary_status_, 0, 256, compute_), "clear canary status");
+  }
   host_ready_.resize(n_tensors, nullptr);
   host_ready_set_.assign(n_tensors, 0);
   grad_ready_.resize(n_tensors, nullptr);
@@ -208,8 +216,29 @@ void OffloadEngine::discard_impl() {
 // Circular allocation.  Live chunks occupy the buffer in allocation order, so the
 // chunks a new allocation runs into are always the oldest ones; they can be evicted
 // once their write-back has been issued (the H2D stream then waits for it to finish).
+void OffloadEngine::arm_guard(char* guard, cudaStream_t stream) {
+  if (guard != nullptr) check(cudaMemsetAsync(guard, 0xA5, kGuardBytes, stream), "arm canary");
+}
+
+void OffloadEngine::verify_guard(const char* guard, int pid) {
+  if (guard != nullptr)
+    check(launch_check_canary(guard, (int)(kGuardBytes / 4), canary_status_, pid, compute_), "check canary");
+}
+
+void OffloadEngine::check_canaries() {
+  if (canary_status_ == nullptr) return;
+  int host[2] = {0, 0};
+  check(cudaMemcpyAsync(host, canary_status_, sizeof(host), cudaMemcpyDeviceToHost, compute_), "read canary status");
+  check(cudaStreamSynchronize(compute_), "sync compute");
+  if (host[0] != 0)
+    throw std::runtime_error("OffloadEngine: a kernel wrote past the staging chunk (or resident buffers) of tensor " +
+                             std::to_string(host[1]) + ": the guard words behind it were overwritten");
+}
+
 OffloadEngine::Entry* OffloadEngine::allocate(size_t bytes, bool may_discard) {
   bytes = up256(bytes);
+  const size_t content = bytes;
+  if (opt_.canaries) bytes += kGuardBytes;
   if (bytes > ring_bytes_) throw std::runtime_error("OffloadEngine: chunk larger than the staging buffer");
   for (int attempt = 0; attempt < 2; ++attempt) {
     size_t start = head_;
@@ -254,6 +283,7 @@ OffloadEngine::Entry* OffloadEngine::allocate(size_t bytes, bool may_discard) {
     e.h2d_done = take_event();
     e.k_done = take_event();
     e.free_ev = take_event();
+    e.guard = opt_.canaries ? ring_ + start + content : nullptr;
     head_ = end;
     return &e;
   }
@@ -300,6 +330,7 @@ OffloadEngine::Entry* OffloadEngine::load_chunk(const StagedStepArgs& a, int64_t
     check(cudaMemcpyAsync(e->x, (const char*)k.extra + xb * off, xb * len, cudaMemcpyHostToDevice, h2d_), "h2d x");
     bytes_h2d_ += xb * len;
   }
+  arm_guard(e->guard, h2d_);
   check(cudaEventRecord(e->h2d_done, h2d_), "record");
   e->pid = a.pid;
   e->eoff = off;
@@ -443,8 +474,8 @@ bool OffloadEngine::make_resident(int pid, int mode, int64_t n) {
   if (!live_.empty() || head_ != 0)
     throw std::runtime_error("OffloadEngine: make_resident after the staging buffer came into use");
   const size_t xb = elem_extra_bytes(mode);
-  const size_t need = 2 * up256(2 * n) + up256(xb * n);
-  if (need + min_ring_bytes(opt_.chunk_elems) > ring_bytes_) return false;
+  const size_t need = 2 * up256(2 * n) + up256(xb * n) + (opt_.canaries ? kGuardBytes : 0);
+  if (need + min_ring_bytes(opt_.chunk_elems) + (opt_.canaries ? kGuardBytes : 0) > ring_bytes_) return false;
   Resident& r = res_[pid];
   r.on = true;
   r.loaded = false;
@@ -453,6 +484,7 @@ bool OffloadEngine::make_resident(int pid, int mode, int64_t n) {
   r.m = ring_;
   r.v = r.m + up256(2 * n);
   r.x = r.v + up256(2 * n);
+  r.guard = opt_.canaries ? r.x + up256(xb * n) : nullptr;
   r.h2d_done = take_event();
   r.k_done = take_event();
   r.free_ev = take_event();
@@ -471,6 +503,7 @@ void OffloadEngine::load_resident(const StagedStepArgs& a, Resident& r) {
   check(cudaMemcpyAsync(r.v, k.v, 2 * r.n, cudaMemcpyHostToDevice, h2d_), "h2d v");
   if (xb) check(cudaMemcpyAsync(r.x, k.extra, xb * r.n, cudaMemcpyHostToDevice, h2d_), "h2d x");
   bytes_h2d_ += (int64_t)((4 + xb) * r.n);
+  arm_guard(r.guard, h2d_);
   check(cudaEventRecord(r.h2d_done, h2d_), "record");
   r.loaded = true;
 }
@@ -503,6 +536,7 @@ void* OffloadEngine::step_resident(const StagedStepArgs& a, Resident& r) {
   c.extra_copy = nullptr;  // the resident master is the device copy
   c.max_ctas = opt_.max_ctas;
   check(launch_chunk(a, c, 0), "adam_step");
+  verify_guard(r.guard, a.pid);
   check(cudaEventRecord(r.k_done, compute_), "record");
 
   WbJob j;
@@ -571,6 +605,7 @@ void* OffloadEngine::staged_step(const StagedStepArgs& a) {
     for (int j = 0; j < k.n_g_peers; ++j) c.g_peers[j] = (const char*)k.g_peers[j] + 2 * off;
     for (int j = 0; j < k.n_p_peers; ++j) c.p_peers[j] = (char*)k.p_peers[j] + 2 * off;
     check(launch_chunk(a, c, off), "adam_step");
+    verify_guard(e->guard, a.pid);
     check(cudaEventRecord(e->k_done, compute_), "record");
 
     WbJob j;
@@ -622,6 +657,7 @@ void OffloadEngine::staged_grad_to_host(int pid, void* host_grad, const void* de
       check(cudaMemcpyAsync(sg, (const char*)host_grad + 2 * off, 2 * len, cudaMemcpyHostToDevice, h2d_), "h2d g");
       bytes_h2d_ += 2 * len;
     }
+    arm_guard(e->guard, h2d_);
     check(cudaEventRecord(e->h2d_done, h2d_), "record");
     check(cudaStreamWaitEvent(compute_, e->h2d_done, 0), "wait h2d");
     AccumArgs acc;
@@ -634,6 +670,7 @@ void OffloadEngine::staged_grad_to_host(int pid, void* host_grad, const void* de
     acc.scratch = scratch;
     acc.max_ctas = opt_.max_ctas;
     check(launch_grad_accumulate(acc, compute_), "grad_accumulate");
+    verify_guard(e->guard, pid);
     check(cudaEventRecord(e->k_done, compute_), "record");
     check(cudaStreamWaitEvent(d2h_, e->k_done, 0), "wait k");
     check(cudaMemcpyAsync((char*)host_grad + 2 * off, sg, 2 * len, cudaMemcpyDeviceToHost, d2h_), "d2h g");
@@ -678,6 +715,7 @@ void OffloadEngine::synchronize() {
   check(cudaStreamSynchronize(compute_), "sync compute");
   check(cudaStreamSynchronize(h2d_), "sync h2d");
   check(cudaStreamSynchronize(d2h_), "sync d2h");
+  check_canaries();
 }
 
 }  // namespace oab

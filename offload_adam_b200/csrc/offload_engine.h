@@ -48,6 +48,12 @@ struct EngineOptions {
   // launched at the pace of the D2H link and whatever the caller wanted to launch next
   // (the next forward pass) waits too.  With the helper thread only that thread blocks.
   bool async_writeback = true;
+  // Debugging aid against kernels that write past their operands: every chunk in the staging
+  // buffer (and every resident tensor) is followed by a 256-byte guard filled with a known
+  // pattern; a small kernel verifies it after the chunk's kernel, and synchronize() raises
+  // when a guard was overwritten (naming the tensor).  Costs one memset and one tiny launch
+  // per chunk.
+  bool canaries = false;
 };
 
 struct StagedStepArgs {
@@ -172,6 +178,7 @@ class OffloadEngine {
     int64_t eoff = 0, len = 0;
     bool has_grad = false;
     char *g = nullptr, *m = nullptr, *v = nullptr, *x = nullptr;  // sub-buffers
+    char* guard = nullptr;  // canary words behind the chunk (EngineOptions::canaries)
   };
   // One chunk's write-back, as handed to the helper thread (everything by value).
   struct WbJob {
@@ -188,13 +195,18 @@ class OffloadEngine {
     bool on = false, loaded = false;
     int mode = 0;
     int64_t n = 0;
-    char *m = nullptr, *v = nullptr, *x = nullptr;
+    char *m = nullptr, *v = nullptr, *x = nullptr, *guard = nullptr;
     cudaEvent_t h2d_done = nullptr, k_done = nullptr, free_ev = nullptr;
     Entry wb;  // stands in for a ring chunk in the write-back job
   };
   void load_resident(const StagedStepArgs& a, Resident& r);
   void* step_resident(const StagedStepArgs& a, Resident& r);
   cudaError_t launch_chunk(const StagedStepArgs& a, const AdamStepArgs& c, int64_t off);
+  void arm_guard(char* guard, cudaStream_t stream);
+  void verify_guard(const char* guard, int pid);
+  void check_canaries();
+  static constexpr size_t kGuardBytes = 256;
+  int* canary_status_ = nullptr;  // device: {flag, pid}; carved from the end of the workspace
   int64_t chunk_of(const StagedStepArgs& a) const { return a.chunk > 0 ? a.chunk : opt_.chunk_elems; }
   int64_t prefetch_impl(const StagedStepArgs& a, int64_t from_off, int64_t max_chunks,
                         int max_inflight, bool* full);

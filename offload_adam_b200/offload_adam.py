@@ -111,6 +111,11 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             finishes before the call that enqueued it returns; no helper threads, no early
             loads.  Results must equal the overlapped run bit for bit; a difference points
             at a missing dependency between streams.
+        debug_canaries: debugging aid against kernels that write past their operands
+            (staged transfer).  Every chunk in the staging buffer and every resident tensor is
+            followed by 256 bytes of a known pattern that a small kernel verifies after the
+            chunk's step; ``synchronize()`` raises, naming the tensor, when a guard was
+            overwritten.
         nvtx: wrap ``step()``, the gradient hooks and the clip reduction in NVTX ranges
             (``oab.*``) for timeline profilers.
         async_writeback: issue the D2H write-backs of the staged transfer from a helper
@@ -162,7 +167,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                  prefetch_policy="eager", verbose=0, *, transfer="auto", grad_residency="auto",
                  device_grad_budget=None, chunk_elems=None, ring_slots=4, max_ctas=0,
                  max_inflight_bytes=8 << 30, staging_bytes=None, prefetch_inflight=2, prefetch_pacing="thread", async_writeback=True,
-                 debug_serialize=False, nvtx=False, seed=None, keep_resident=True):
+                 debug_serialize=False, nvtx=False, seed=None, keep_resident=True, debug_canaries=False):
         if prefetch_policy not in ("eager", "lazy"):
             raise ValueError(f"prefetch_policy must be 'eager' or 'lazy' (got {prefetch_policy!r})")
         if grad_residency not in ("auto", "host", "device"):
@@ -274,7 +279,7 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             self.device, mode, len(params), transfer=transfer, chunk_elems=chunk_elems,
             ring_slots=ring_slots, max_ctas=max_ctas, max_inflight_bytes=max_inflight_bytes,
             staging_bytes=self._resolve_staging_bytes(staging_bytes),
-            async_writeback=async_writeback, serialize=debug_serialize,
+            async_writeback=async_writeback, serialize=debug_serialize, canaries=debug_canaries,
         )
         self.transfer = self._engine.transfer
         self.h2d_stream = self._engine.h2d_stream

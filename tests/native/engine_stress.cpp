@@ -31,6 +31,8 @@ cudaError_t launch_adam_step(const AdamStepArgs& a, cudaStream_t s) {
       if (x) x[i] += 3.0f + (g ? (float)g[i] : 0.0f);
       if (p) p[i] = m[i];
     }
+    // deliberate overrun (canary scenario): the first word behind the chunk's last sub-buffer
+    if (c.max_ctas == -7 && x) x[((4 * c.n + 255) / 256 * 256) / 4] = 1.0f;
   });
   return cudaSuccess;
 }
@@ -51,6 +53,17 @@ cudaError_t launch_adam_quant_push(const AdamStepArgs& a, const QuantPushArgs& q
   });
   return cudaSuccess;
 }
+// stand-in for the guard check (the real one is a kernel in grad_ops.cu)
+cudaError_t launch_check_canary(const void* guard, int words, int* status, int tag, cudaStream_t s) {
+  s->push([=] {
+    const uint32_t* g = static_cast<const uint32_t*>(guard);
+    for (int i = 0; i < words; ++i)
+      if (g[i] != kCanaryWord && status[0] == 0) { status[0] = 1; status[1] = tag; }
+  });
+  return cudaSuccess;
+}
+// when set, the stand-in step kernel of this tensor writes one element past its moments
+static std::atomic<int> g_overrun_pid{-1};
 // stand-in accumulate: out = a + b (uint16 arithmetic)
 cudaError_t launch_grad_accumulate(const AccumArgs& a, cudaStream_t s) {
   AccumArgs c = a;
@@ -91,6 +104,8 @@ struct Scenario {
   bool chaos = false;  // skipped tensors, repeated and cancelled plans, discards between steps
   int slow_h2d_us = 0, slow_d2h_us = 0;  // extra time per operation of the copy streams
   int resident = 0;    // this many tensors (the last ones) keep their state in the staging buffer
+  bool canaries = false;  // guard words behind every chunk and resident tensor
+  bool overrun = false;   // the stand-in kernel writes past its operands: synchronize() must say so
   bool quant = false;  // tensors are whole rows of kInF elements, stepped through the quantizing launch
                        // in chunks of their own size
 };
@@ -119,14 +134,18 @@ static int run(const Scenario& sc, unsigned seed) {
   oab::EngineOptions opt;
   opt.chunk_elems = sc.chunk;
   opt.async_writeback = sc.async_writeback;
+  opt.canaries = sc.canaries;
+  if (sc.overrun) opt.max_ctas = -7;
+  bool caught = false;
   size_t ring = OffloadEngine::min_ring_bytes(sc.chunk);
   if (sc.ring_fraction > 0) ring = std::max(ring, (size_t)(state_bytes * sc.ring_fraction) / 256 * 256);
   size_t resident_need = 0;
   for (int t = sc.tensors - sc.resident; t < sc.tensors; ++t)
     resident_need += 2 * ((2 * ts[t].n + 255) / 256 * 256) + (4 * ts[t].n + 255) / 256 * 256;
-  ring += resident_need;
+  ring += resident_need + (sc.canaries ? 256 * (size_t)(sc.resident + 8) : 0);
   void* ws = aligned_alloc(256, ring);
   int bad = 0;
+  try {
   // per-tensor chunk of the quantized stand-ins: whole rows, not the engine's default
   const int64_t qchunk = sc.quant ? std::max<int64_t>(kInF, (sc.chunk - 3) / kInF * kInF) : 0;
   {
@@ -213,6 +232,16 @@ static int run(const Scenario& sc, unsigned seed) {
     }
     if (!sc.destroy_busy) eng.synchronize();
   }
+  } catch (const std::runtime_error& e) {
+    if (sc.overrun && std::string(e.what()).find("guard") != std::string::npos) caught = true;
+    else { fprintf(stderr, "%s: unexpected error: %s\n", sc.name, e.what()); ++bad; }
+  }
+  if (sc.overrun) {
+    if (!caught) { fprintf(stderr, "%s: the overrun was not reported\n", sc.name); ++bad; }
+    free(ws);
+    printf("%-28s seed %u: %s\n", sc.name, seed, bad ? "FAILED" : "ok (overrun reported)");
+    return bad;
+  }
   for (int t = 0; t < sc.tensors; ++t) {
     const Tensor& T = ts[t];
     for (int64_t i = 0; i < T.n; ++i) {
@@ -260,9 +289,15 @@ int main(int argc, char** argv) {
       {"resident, chaos",               9, 10,  32, 0.5,  true,  true,  false, true,  12, false, false, true,  0, 0,   5},
       {"resident, slow write-backs",    8, 5,   64, 0.3,  true,  true,  false, false, 12, false, false, false, 0, 150, 4},
       {"resident, destroyed busy",      8, 4,   64, 0.3,  true,  true,  false, false, 16, false, true,  false, 0, 0,   4},
-      {"row chunks, quantizing launch", 8, 5,   64, 0.4,  true,  true,  false, false, 16, false, false, false, 0, 0,   0, true},
-      {"row chunks, resident",          8, 5,   64, 0.4,  true,  true,  false, true,  16, false, false, false, 0, 0,   3, true},
-      {"row chunks, caller loads",      7, 5,   64, 0.6,  true,  false, true,  false, 32, false, false, false, 0, 0,   0, true},
+      {"row chunks, quantizing launch", 8, 5,   64, 0.4,  true,  true,  false, false, 16, false, false, false, 0, 0,   0, false, false, true},
+      {"row chunks, resident",          8, 5,   64, 0.4,  true,  true,  false, true,  16, false, false, false, 0, 0,   3, false, false, true},
+      {"row chunks, caller loads",      7, 5,   64, 0.6,  true,  false, true,  false, 32, false, false, false, 0, 0,   0, false, false, true},
+      //                                                                                                                    resident canaries overrun quant
+      {"canaries, ring",                8, 5,   64, 0.4,  true,  true,  false, false, 16, false, false, false, 0, 0,   0, true},
+      {"canaries, resident + ring",     8, 5,   64, 0.3,  true,  true,  false, true,  16, false, false, false, 0, 0,   4, true},
+      {"canaries, host gradients",      6, 5,   64, 0.3,  true,  true,  false, false, 16, true,  false, false, 0, 0,   0, true},
+      {"canaries report an overrun",    6, 3,   64, 0.5,  false, false, false, false, 64, false, false, false, 0, 0,   0, true, true},
+      {"canaries, resident overrun",    6, 3,   64, 0.5,  true,  true,  false, false, 16, false, false, false, 0, 0,   6, true, true},
   };
   int bad = 0;
   for (int r = 0; r < rounds; ++r)

@@ -166,3 +166,23 @@ def test_resume_reloads_resident_state():
     o_a.synchronize()
     o_b.synchronize()
     same(m_a, o_a, m_b, o_b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("staging", [1 << 20, 0])
+def test_guard_words_stay_intact_and_do_not_change_results(staging):
+    """``debug_canaries=True`` puts a guard behind every staging chunk and resident tensor and
+    verifies it after each step kernel: the kernels must leave them intact (``synchronize()``
+    would raise), and the run must equal one without guards bit for bit.  That an overwritten
+    guard is reported is tested against the stand-in runtime (tests/native/engine_stress.cpp)."""
+    device = "cuda"
+    batches = data(8, device)
+    m_a, m_b = net(device), net(device)
+    o_a = OffloadAdam(m_a, max_grad_norm=0.05, staging_bytes=staging, **KW)
+    o_b = OffloadAdam(m_b, max_grad_norm=0.05, staging_bytes=staging, debug_canaries=True, **KW)
+    for s in range(4):
+        one_step(m_a, o_a, batches[2 * s:2 * s + 2])
+        one_step(m_b, o_b, batches[2 * s:2 * s + 2])
+    o_a.synchronize()
+    o_b.synchronize()
+    same(m_a, o_a, m_b, o_b)

@@ -441,3 +441,52 @@ def test_model_built_in_symmetric_memory_is_adopted():
         mp.spawn(_adopt_worker, args=(2, free_port(), d), nprocs=2, join=True)
         reports = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(2)]
     assert all(r["ok"] for r in reports), reports
+
+
+# ------------- torch.distributed back end with gradients on the host (both gradient layouts)
+def _host_grad_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    report = {}
+    try:
+        from offload_adam_b200 import DistributedOffloadAdam
+        ga, steps = 3, 3
+        for layout in ("full", "shard"):
+            for clip in (None, 0.05):
+                results = {}
+                for residency in ("host", "device"):
+                    model = make_net(device)
+                    opt = DistributedOffloadAdam(model, lr=1e-2, weight_decay=0.05, mode="fp32_master",
+                                                 max_grad_norm=clip, decoupled_weight_decay=True,
+                                                 inplace_param_threshold=2000, comm="nccl", grad_layout=layout,
+                                                 grad_residency=residency, chunk_elems=4096, ring_slots=3)
+                    assert opt.comm == "nccl" and opt.grad_residency == residency
+                    data = rank_batches(rank, ga * steps, device)
+                    k = 0
+                    for _ in range(steps):
+                        for micro in range(ga):
+                            opt.ready_for_optimizer_step = micro == ga - 1
+                            (model(data[k]).float().pow(2).mean() / ga).backward()
+                            k += 1
+                        opt.step()
+                    opt.synchronize()
+                    results[residency] = [p.detach().clone() for p in model.parameters()]
+                # the kernels that read the pinned gradient buffer wait for the copy that filled it:
+                # gradients parked on the host must give the bits of gradients kept in HBM
+                report[f"{layout}/{clip}"] = all(torch.equal(a, b)
+                                                 for a, b in zip(results["host"], results["device"]))
+    finally:
+        torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
+        dist.destroy_process_group()
+
+
+def test_host_resident_gradients_on_the_collective_path_match_device_resident_ones():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_host_grad_worker, args=(2, free_port(), d), nprocs=2, join=True)
+        reports = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(2)]
+    for rep in reports:
+        assert len(rep) == 4 and all(rep.values()), rep
