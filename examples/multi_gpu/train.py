@@ -31,7 +31,7 @@ def main():
     p.add_argument("--comm", choices=["auto", "symm", "nccl"], default="auto")
     p.add_argument("--grad-layout", choices=["full", "shard"], default="full",
                    help="'shard': reduce-scatter every micro-batch and accumulate only this rank's rows "
-                        "(gradient memory divided by the world size; uses the torch.distributed collectives)")
+                        "(gradient memory divided by the world size; what a 70B model needs)")
     args = p.parse_args()
     common.validate(args)
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
