@@ -69,6 +69,9 @@ def parse_args():
     ap.add_argument("--model-impl", choices=["own", "hf"], default="own",
                     help="this framework's arm: the package's Llama, or the HuggingFace module the reference arm trains")
     ap.add_argument("--no-resident", action="store_true", help="stream all optimizer state every step")
+    ap.add_argument("--resident-writeback", default="step", choices=["step", "on_demand"],
+                    help="'on_demand': resident state is copied to the host only when the host copy is "
+                         "asked for (here: once, at the end of the timed region); not the default")
     ap.add_argument("--symmetric-model", action="store_true",
                     help="create the large parameters directly in symmetric memory (default for llama3-70b with "
                          "more than one GPU: a second copy of the weights would not fit)")
@@ -247,6 +250,8 @@ def build_ours(args, preset, device):
         common["prefetch_inflight"] = args.prefetch_inflight
     if args.no_resident:
         common["keep_resident"] = False
+    if args.resident_writeback != "step":
+        common["resident_writeback"] = args.resident_writeback
     if preset["optimizer"] == "distributed":
         opt = DistributedOffloadAdam(model, comm=args.comm, grad_layout=args.grad_layout, **common)
     else:
@@ -518,6 +523,7 @@ def main():
                 "quant": args.quant,
                 "staging_gib": (getattr(getattr(opt, "_engine", None), "staging_bytes", 0) or 0) / 2**30,
                 "resident_gib": (getattr(getattr(opt, "_engine", None), "resident_bytes", 0) or 0) / 2**30,
+                "resident_writeback": getattr(opt, "resident_writeback", None),
                 "model_impl": args.model_impl if args.impl == "ours" else "hf",
             },
             "optimizer_link_bytes_per_step": link_bytes,

@@ -305,13 +305,14 @@ struct PyEngine {
   // the engine (helper threads, copies in flight) must be gone before the buffer is
   ~PyEngine() { eng.reset(); }
   PyEngine(int64_t device, int64_t compute, int64_t h2d, int64_t d2h, Tensor ws, int64_t chunk_elems,
-           int64_t max_ctas, int64_t n_tensors, bool async_writeback, bool canaries)
+           int64_t max_ctas, int64_t n_tensors, bool async_writeback, bool canaries, bool lazy_resident)
       : workspace(std::move(ws)) {
     oab::EngineOptions o;
     o.chunk_elems = chunk_elems;
     o.max_ctas = (int)max_ctas;
     o.async_writeback = async_writeback;
     o.canaries = canaries;
+    o.lazy_resident = lazy_resident;
     TORCH_CHECK(workspace.is_cuda(), "engine workspace must be a CUDA tensor");
     eng = std::make_unique<oab::OffloadEngine>(
         (int)device, reinterpret_cast<cudaStream_t>(compute), reinterpret_cast<cudaStream_t>(h2d),
@@ -498,10 +499,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("QDT_F16") = (int)oab::kF16;
 
   py::class_<PyEngine>(m, "OffloadEngine")
-      .def(py::init<int64_t, int64_t, int64_t, int64_t, Tensor, int64_t, int64_t, int64_t, bool, bool>(),
+      .def(py::init<int64_t, int64_t, int64_t, int64_t, Tensor, int64_t, int64_t, int64_t, bool, bool, bool>(),
            py::arg("device"), py::arg("compute"), py::arg("h2d"), py::arg("d2h"), py::arg("workspace"),
            py::arg("chunk_elems"), py::arg("max_ctas"), py::arg("n_tensors"), py::arg("async_writeback"),
-           py::arg("canaries") = false)
+           py::arg("canaries") = false, py::arg("lazy_resident") = false)
       .def_static("min_ring_bytes", [](int64_t chunk_elems) {
         return (int64_t)oab::OffloadEngine::min_ring_bytes(chunk_elems);
       })

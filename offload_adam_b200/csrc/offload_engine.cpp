@@ -200,8 +200,12 @@ void OffloadEngine::drain_writer() {
 
 void OffloadEngine::discard_prefetched() {
   stop_prefetch();
+  // resident state the host has not seen yet goes back first (lazy write-back): the
+  // reload below then reads it again, and no step is ever lost
+  flush_resident();
   discard_impl();
-  // the host copy was changed behind the engine's back: resident state is stale too
+  // the host copy may change behind the engine's back from here on: resident state is
+  // loaded again at its next step, behind the write-back above
   for (Resident& r : res_) r.loaded = false;
 }
 
@@ -539,19 +543,32 @@ void* OffloadEngine::step_resident(const StagedStepArgs& a, Resident& r) {
   verify_guard(r.guard, a.pid);
   check(cudaEventRecord(r.k_done, compute_), "record");
 
+  r.hm = k.m; r.hv = k.v; r.hx = xb ? k.extra : nullptr;
+  if (opt_.lazy_resident) r.dirty = true;
+  else writeback_resident(a.pid, r);
+  return (a.quant != nullptr && a.quant->format == kQNVFP4) ? (void*)r.x : nullptr;
+}
+
+void OffloadEngine::writeback_resident(int pid, Resident& r) {
+  const size_t xb = elem_extra_bytes(r.mode);
   WbJob j;
   r.wb.retired.store(false, std::memory_order_relaxed);
   j.e = &r.wb;
   j.k_done = r.k_done;
   j.free_ev = r.free_ev;
-  j.host[0] = k.m; j.dev[0] = r.m; j.bytes[0] = 2 * r.n;
-  j.host[1] = k.v; j.dev[1] = r.v; j.bytes[1] = 2 * r.n;
+  j.host[0] = r.hm; j.dev[0] = r.m; j.bytes[0] = 2 * r.n;
+  j.host[1] = r.hv; j.dev[1] = r.v; j.bytes[1] = 2 * r.n;
   j.n = 2;
-  if (xb) { j.host[2] = k.extra; j.dev[2] = r.x; j.bytes[2] = xb * r.n; j.n = 3; }
+  if (xb) { j.host[2] = r.hx; j.dev[2] = r.x; j.bytes[2] = xb * r.n; j.n = 3; }
   bytes_d2h_ += (int64_t)((4 + xb) * r.n);
-  j.pid = a.pid;
+  j.pid = pid;
+  r.dirty = false;
   submit_writeback(j);
-  return (a.quant != nullptr && a.quant->format == kQNVFP4) ? (void*)r.x : nullptr;
+}
+
+void OffloadEngine::flush_resident() {
+  for (size_t i = 0; i < res_.size(); ++i)
+    if (res_[i].on && res_[i].dirty) writeback_resident((int)i, res_[i]);
 }
 
 void* OffloadEngine::staged_step(const StagedStepArgs& a) {
@@ -705,12 +722,14 @@ void OffloadEngine::join_compute(cudaStream_t stream) {
 }
 
 void OffloadEngine::wait_writebacks() {
+  flush_resident();
   drain_writer();
   check(cudaStreamSynchronize(d2h_), "sync d2h");
 }
 
 void OffloadEngine::synchronize() {
   stop_prefetch();
+  flush_resident();
   drain_writer();
   check(cudaStreamSynchronize(compute_), "sync compute");
   check(cudaStreamSynchronize(h2d_), "sync h2d");

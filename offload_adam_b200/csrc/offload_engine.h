@@ -54,6 +54,9 @@ struct EngineOptions {
   // when a guard was overwritten (naming the tensor).  Costs one memset and one tiny launch
   // per chunk.
   bool canaries = false;
+  // Resident state is copied back to the host only when somebody asks for the host copy
+  // (wait_writebacks, synchronize) instead of after every step.
+  bool lazy_resident = false;
 };
 
 struct StagedStepArgs {
@@ -198,7 +201,12 @@ class OffloadEngine {
     char *m = nullptr, *v = nullptr, *x = nullptr, *guard = nullptr;
     cudaEvent_t h2d_done = nullptr, k_done = nullptr, free_ev = nullptr;
     Entry wb;  // stands in for a ring chunk in the write-back job
+    // lazy write-back: the host addresses of the last step, copied to at the next flush
+    bool dirty = false;
+    void *hm = nullptr, *hv = nullptr, *hx = nullptr;
   };
+  void writeback_resident(int pid, Resident& r);
+  void flush_resident();
   void load_resident(const StagedStepArgs& a, Resident& r);
   void* step_resident(const StagedStepArgs& a, Resident& r);
   cudaError_t launch_chunk(const StagedStepArgs& a, const AdamStepArgs& c, int64_t off);

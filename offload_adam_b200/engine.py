@@ -35,7 +35,7 @@ from .ops.oracle import MODE_IDS, beta_hat
 class TransferEngine:
     def __init__(self, device, mode, n_tensors, transfer="auto", chunk_elems=8 << 20, ring_slots=4,
                  max_ctas=0, max_inflight_bytes=8 << 30, staging_bytes=0, async_writeback=True,
-                 serialize=False, canaries=False):
+                 serialize=False, canaries=False, lazy_resident=False):
         self.device = torch.device(device)
         self.mode = mode
         self.mode_id = MODE_IDS[mode]
@@ -98,6 +98,7 @@ class TransferEngine:
                         self.device.index or 0, self.opt_stream.cuda_stream,
                         self.h2d_stream.cuda_stream, self.d2h_stream.cuda_stream, ws,
                         chunk_elems, self.max_ctas, n_tensors, bool(async_writeback), bool(canaries),
+                        bool(lazy_resident),
                     )
 
     # ------------------------------------------------------------ stream glue

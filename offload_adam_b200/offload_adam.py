@@ -138,6 +138,12 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
             When the buffer cannot hold everything, the tensors that are stepped last
             stay and the others stream through the rest of the buffer.  ``False``
             streams everything every step.
+        resident_writeback: ``'step'`` (default) copies resident state back to the host after
+            every step.  ``'on_demand'`` copies it back only when the host copy is asked for
+            (``state_dict()``, ``synchronize()``, ``wait_writeback()``, ``close()``): between
+            those calls the resident tensors' host buffers are stale and nothing of them
+            crosses the host link in either direction, like the small tensors that
+            ``inplace_param_threshold`` keeps on the GPU.
         max_ctas: grid cap of the streaming kernels (0: kernel default); small
             values leave the SMs to the concurrent backward GEMMs.
         seed: seeds the stochastic-rounding stream.
@@ -167,7 +173,8 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
                  prefetch_policy="eager", verbose=0, *, transfer="auto", grad_residency="auto",
                  device_grad_budget=None, chunk_elems=None, ring_slots=4, max_ctas=0,
                  max_inflight_bytes=8 << 30, staging_bytes=None, prefetch_inflight=2, prefetch_pacing="thread", async_writeback=True,
-                 debug_serialize=False, nvtx=False, seed=None, keep_resident=True, debug_canaries=False):
+                 debug_serialize=False, nvtx=False, seed=None, keep_resident=True, debug_canaries=False,
+                 resident_writeback="step"):
         if prefetch_policy not in ("eager", "lazy"):
             raise ValueError(f"prefetch_policy must be 'eager' or 'lazy' (got {prefetch_policy!r})")
         if grad_residency not in ("auto", "host", "device"):
@@ -274,12 +281,16 @@ class OffloadAdam(MasterLoadingMixin, Optimizer):
         self.prefetch_inflight = int(prefetch_inflight)
         if prefetch_pacing not in ("thread", "hooks"):
             raise ValueError(f"prefetch_pacing must be 'thread' or 'hooks', got {prefetch_pacing!r}")
+        if resident_writeback not in ("step", "on_demand"):
+            raise ValueError(f"resident_writeback must be 'step' or 'on_demand', got {resident_writeback!r}")
+        self.resident_writeback = resident_writeback
         self.prefetch_pacing = prefetch_pacing
         self._engine = TransferEngine(
             self.device, mode, len(params), transfer=transfer, chunk_elems=chunk_elems,
             ring_slots=ring_slots, max_ctas=max_ctas, max_inflight_bytes=max_inflight_bytes,
             staging_bytes=self._resolve_staging_bytes(staging_bytes),
             async_writeback=async_writeback, serialize=debug_serialize, canaries=debug_canaries,
+            lazy_resident=resident_writeback == "on_demand",
         )
         self.transfer = self._engine.transfer
         self.h2d_stream = self._engine.h2d_stream

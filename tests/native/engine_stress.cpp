@@ -108,6 +108,7 @@ struct Scenario {
   bool overrun = false;   // the stand-in kernel writes past its operands: synchronize() must say so
   bool quant = false;  // tensors are whole rows of kInF elements, stepped through the quantizing launch
                        // in chunks of their own size
+  bool lazy = false;   // resident state goes back to the host only at wait_writebacks()/synchronize()
 };
 
 static int run(const Scenario& sc, unsigned seed) {
@@ -135,6 +136,7 @@ static int run(const Scenario& sc, unsigned seed) {
   opt.chunk_elems = sc.chunk;
   opt.async_writeback = sc.async_writeback;
   opt.canaries = sc.canaries;
+  opt.lazy_resident = sc.lazy;
   if (sc.overrun) opt.max_ctas = -7;
   bool caught = false;
   size_t ring = OffloadEngine::min_ring_bytes(sc.chunk);
@@ -298,6 +300,12 @@ int main(int argc, char** argv) {
       {"canaries, host gradients",      6, 5,   64, 0.3,  true,  true,  false, false, 16, true,  false, false, 0, 0,   0, true},
       {"canaries report an overrun",    6, 3,   64, 0.5,  false, false, false, false, 64, false, false, false, 0, 0,   0, true, true},
       {"canaries, resident overrun",    6, 3,   64, 0.5,  true,  true,  false, false, 16, false, false, false, 0, 0,   6, true, true},
+      //                                                                                                                    resident canaries overrun quant lazy
+      {"lazy resident, all",            6, 8,   64, 0.0,  true,  true,  false, false, 16, false, false, false, 0, 0,   6, false, false, false, true},
+      {"lazy resident + ring",          9, 8,   32, 0.15, true,  true,  false, true,  8,  false, false, false, 0, 0,   4, false, false, false, true},
+      {"lazy resident, inline",         6, 6,   64, 0.0,  false, false, false, false, 64, false, false, false, 0, 0,   3, false, false, false, true},
+      {"lazy resident, chaos",          9, 10,  32, 0.5,  true,  true,  false, true,  12, false, false, true,  0, 0,   5, false, false, false, true},
+      {"lazy resident, quantized",      8, 6,   64, 0.4,  true,  true,  false, true,  16, false, false, false, 0, 0,   3, true,  false, true,  true},
   };
   int bad = 0;
   for (int r = 0; r < rounds; ++r)

@@ -146,6 +146,52 @@ def test_resident_state_equals_streamed_state(clip, staging):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("staging", [1 << 20, 300 * 1024])
+def test_on_demand_writeback_of_resident_state(staging):
+    """``resident_writeback='on_demand'``: resident state stays on the GPU between steps
+    (no write-back traffic for it), the host copy is made current by ``wait_writeback()``,
+    ``state_dict()`` and a resume, and every step computes the same bits as with a
+    write-back per step."""
+    device = "cuda"
+    batches = data(10, device)
+    m_a, m_b = net(device), net(device)
+    o_a = OffloadAdam(m_a, max_grad_norm=0.05, staging_bytes=staging, **KW)
+    o_b = OffloadAdam(m_b, max_grad_norm=0.05, staging_bytes=staging, resident_writeback="on_demand", **KW)
+    assert len(o_a._resident) == len(o_b._resident) > 0
+    for s in range(3):
+        one_step(m_a, o_a, batches[2 * s:2 * s + 2])
+        one_step(m_b, o_b, batches[2 * s:2 * s + 2])
+    torch.cuda.synchronize()
+    _, d2h_a = o_a._engine.bytes_moved()
+    _, d2h_b = o_b._engine.bytes_moved()
+    assert d2h_b < d2h_a
+    o_a.wait_writeback()
+    o_b.wait_writeback()       # the resident tensors go back now, once
+    same(m_a, o_a, m_b, o_b)
+    _, d2h_b2 = o_b._engine.bytes_moved()
+    assert d2h_b2 > d2h_b and d2h_b2 < d2h_a
+    # a state_dict() in the middle of training and a resume into the lazy optimizer
+    one_step(m_a, o_a, batches[6:8])
+    one_step(m_b, o_b, batches[6:8])
+    sd_a, sd_b = o_a.state_dict(), o_b.state_dict()
+    for sa, sb in zip(sd_a["state"].values(), sd_b["state"].values()):
+        for k in sa:
+            if torch.is_tensor(sa[k]):
+                assert torch.equal(sa[k].cpu(), sb[k].cpu()), k
+    o_b.load_offload_state_dict(copy.deepcopy(sd_a))
+    one_step(m_a, o_a, batches[8:10])
+    one_step(m_b, o_b, batches[8:10])
+    o_a.synchronize()
+    o_b.synchronize()
+    same(m_a, o_a, m_b, o_b)
+
+
+def test_unknown_resident_writeback_is_rejected():
+    with pytest.raises(ValueError, match="resident_writeback"):
+        OffloadAdam(net("cpu"), resident_writeback="never", **KW)
+
+
+@pytest.mark.gpu
 def test_resume_reloads_resident_state():
     device = "cuda"
     batches = data(8, device)
