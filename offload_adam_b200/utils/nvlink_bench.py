@@ -117,8 +117,11 @@ def run_cases(args):
     out.append({"case": "adam_push", "nvlink_bytes_out": remote, "ms": t, "GBs_out": remote / t / 1e6,
                 "fraction_of_link_reference": remote / t / 1e6 / link, "local_hbm_GBs": hbm})
     t = _events_ms(lambda: adam(None, my_g, my_p), args.iters)
-    out.append({"case": "pull_adam_push", "nvlink_bytes_in": remote, "nvlink_bytes_out": remote, "ms": t,
-                "GBs_each_direction": remote / t / 1e6, "fraction_of_link_reference": remote / t / 1e6 / link})
+    # every rank runs the same launch: a rank's inbound link carries the gradients it pulls AND
+    # the parameters the others push into it (outbound: what it serves and what it pushes)
+    out.append({"case": "pull_adam_push", "nvlink_bytes_in": 2 * remote, "nvlink_bytes_out": 2 * remote, "ms": t,
+                "GBs_each_direction": 2 * remote / t / 1e6,
+                "fraction_of_link_reference": 2 * remote / t / 1e6 / link})
 
     # ---- quantized weight: rows x cols, this rank owns rows/world of them
     cols = args.cols
