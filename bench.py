@@ -68,6 +68,9 @@ def parse_args():
     ap.add_argument("--model", choices=["llama3-8b", "llama3-70b", "tiny"], default="llama3-8b")
     ap.add_argument("--model-impl", choices=["own", "hf"], default="own",
                     help="this framework's arm: the package's Llama, or the HuggingFace module the reference arm trains")
+    ap.add_argument("--hf-chunked-loss", action="store_true",
+                    help="with --model-impl hf: head and loss chunk by chunk (models.hf.causal_lm_loss) instead "
+                         "of the module's own full-logits loss")
     ap.add_argument("--no-resident", action="store_true", help="stream all optimizer state every step")
     ap.add_argument("--resident-writeback", default="step", choices=["step", "on_demand"],
                     help="'on_demand': resident state is copied to the host only when the host copy is "
@@ -257,7 +260,12 @@ def build_ours(args, preset, device):
     else:
         opt = OffloadAdam(model, **common)
 
-    if args.model_impl == "hf":
+    if args.model_impl == "hf" and args.hf_chunked_loss:
+        from offload_adam_b200.models.hf import causal_lm_loss
+
+        def loss_fn(ids):
+            return causal_lm_loss(model, ids, ids)
+    elif args.model_impl == "hf":
         def loss_fn(ids):
             return model(input_ids=ids, labels=ids).loss
     else:
@@ -524,7 +532,8 @@ def main():
                 "staging_gib": (getattr(getattr(opt, "_engine", None), "staging_bytes", 0) or 0) / 2**30,
                 "resident_gib": (getattr(getattr(opt, "_engine", None), "resident_bytes", 0) or 0) / 2**30,
                 "resident_writeback": getattr(opt, "resident_writeback", None),
-                "model_impl": args.model_impl if args.impl == "ours" else "hf",
+                "model_impl": (args.model_impl + ("+chunked_loss" if args.hf_chunked_loss and args.model_impl == "hf" else ""))
+                if args.impl == "ours" else "hf",
             },
             "optimizer_link_bytes_per_step": link_bytes,
             "exposed_opt_ms": exposed_ms, "peak_gpu_gb": peak_gb, "build_s": t_build,

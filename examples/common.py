@@ -12,6 +12,7 @@ import torch
 
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
+from offload_adam_b200.models.hf import causal_lm_loss  # noqa: E402
 from offload_adam_b200.models.llama import (build_llama, llama3_8b, llama3_70b,  # noqa: E402
                                             qwen3_8b, tiny_llama)
 
@@ -25,6 +26,9 @@ def add_common_args(p):
                    help="train a HuggingFace causal LM instead of the package's own Llama: a local checkpoint "
                         "directory or hub id (weights are loaded with AutoModelForCausalLM.from_pretrained), or "
                         "a directory / file holding only a config.json (random-init weights of that architecture)")
+    p.add_argument("--full-logits", action="store_true",
+                   help="with --hf-model: use the module's own loss (full fp32 logits) instead of the chunked "
+                        "linear cross-entropy that never materialises them")
     p.add_argument("--layers", type=int, default=None, help="override the number of layers")
     p.add_argument("--mode", choices=MODES, default="fp32_master")
     p.add_argument("--tokens-per-sample", type=int, default=2048)
@@ -67,15 +71,20 @@ def validate(args):
 
 class _HFCausalLM(torch.nn.Module):
     """Gives a HuggingFace causal LM the call signature the example loop uses
-    (``model(ids, labels=ids)`` returns the loss) and keeps ``.config`` reachable."""
+    (``model(ids, labels=ids)`` returns the loss) and keeps ``.config`` reachable.  The
+    head and the loss run chunk by chunk (``offload_adam_b200.models.hf.causal_lm_loss``)
+    unless ``full_logits`` asks for the module's own loss."""
 
-    def __init__(self, hf):
+    def __init__(self, hf, full_logits=False):
         super().__init__()
         self.hf = hf
         self.config = hf.config
+        self.full_logits = full_logits
 
     def forward(self, ids, labels=None):
-        return self.hf(input_ids=ids, labels=labels).loss
+        if self.full_logits or labels is None:
+            return self.hf(input_ids=ids, labels=labels).loss
+        return causal_lm_loss(self.hf, ids, labels)
 
     def gradient_checkpointing_enable(self):
         self.hf.gradient_checkpointing_enable()
@@ -109,7 +118,7 @@ def build_hf_model(args, device):
     else:
         hf = AutoModelForCausalLM.from_pretrained(src, dtype=torch.bfloat16, attn_implementation="sdpa")
         hf.config.use_cache = False
-    model = _HFCausalLM(hf.to(torch.bfloat16).to(device))
+    model = _HFCausalLM(hf.to(torch.bfloat16).to(device), full_logits=getattr(args, "full_logits", False))
     model.train()
     if args.gradient_checkpointing:
         model.gradient_checkpointing_enable()

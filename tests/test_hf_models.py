@@ -108,3 +108,34 @@ def test_qat_on_hf_llama_and_export(device, cls, tmp_path):
     with safe_open(str(files[0]), "pt") as f:
         keys = set(f.keys())
     assert "model.layers.0.mlp.up_proj.weight_packed" in keys and "model.layers.0.mlp.up_proj.weight" not in keys
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("tied", [False, True])
+def test_chunked_loss_of_hf_model_equals_its_own_loss(device, tied):
+    """``causal_lm_loss`` (decoder as usual, head and loss chunk by chunk) against the
+    module's own full-logits loss: same value, same gradients, also with tied embeddings
+    and ignored labels."""
+    from offload_adam_b200.models.hf import causal_lm_loss, supports_chunked_loss
+    cfg = transformers.LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+                                   tie_word_embeddings=tied, attn_implementation="sdpa", use_cache=False)
+    torch.manual_seed(0)
+    model = transformers.LlamaForCausalLM(cfg).to(torch.float32).to(device).train()
+    assert supports_chunked_loss(model)
+    ids = token_batches(1, device)[0]
+    labels = ids.clone()
+    labels[0, 5:9] = -100
+    want = model(input_ids=ids, labels=labels).loss
+    want.backward()
+    g_want = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad(set_to_none=True)
+    got = causal_lm_loss(model, ids, labels, chunk=24)   # 64 rows: two full chunks and a tail
+    got.backward()
+    torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
+    for n, p in model.named_parameters():
+        torch.testing.assert_close(p.grad, g_want[n], rtol=2e-4, atol=1e-6, msg=n)
+    # a head this function cannot take apart falls back to the module's own loss
+    model.lm_head.bias = torch.nn.Parameter(torch.zeros(512, device=device))
+    assert not supports_chunked_loss(model)
+    torch.testing.assert_close(causal_lm_loss(model, ids, labels), model(input_ids=ids, labels=labels).loss)
