@@ -29,6 +29,9 @@ def add_common_args(p):
     p.add_argument("--full-logits", action="store_true",
                    help="with --hf-model: use the module's own loss (full fp32 logits) instead of the chunked "
                         "linear cross-entropy that never materialises them")
+    p.add_argument("--liger-fused-linear-ce", action="store_true",
+                   help="accepted so that the reference trainers' command lines keep working; the chunked linear "
+                        "cross-entropy is the default here and needs no extra package")
     p.add_argument("--layers", type=int, default=None, help="override the number of layers")
     p.add_argument("--mode", choices=MODES, default="fp32_master")
     p.add_argument("--tokens-per-sample", type=int, default=2048)
